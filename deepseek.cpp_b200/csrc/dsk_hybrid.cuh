@@ -89,11 +89,87 @@ __global__ void convert_kernel(const ST* __restrict__ src, DT* __restrict__ dst,
 __global__ void set_ctl(int* ctl, int pos0) { ctl[0] = pos0; }
 __global__ void advance_ctl(int* ctl, int by) { ctl[0] += by; }
 
+// x[t] = scale * table[tok[t]] (+ bigram[row]).  The second table is indexed by the pair (previous token, token): row
+// (prev * mul_prev + tok * mul_cur) mod buckets, and row `buckets` for the first token of a sequence (position ctl[0] + t == 0).
+// The token before the step's first one is carried[0]; carry_token stores the step's last token there afterwards.
 template <typename WT>
-__global__ void embed_rows(const int* __restrict__ tok, const WT* __restrict__ table, int width, float* __restrict__ x) {
+__global__ void embed_rows(const int* __restrict__ tok, const WT* __restrict__ table, int width, float* __restrict__ x, float scale,
+                           const WT* __restrict__ bigram, int buckets, int mul_prev, int mul_cur, const int* __restrict__ ctl,
+                           const int* __restrict__ carried) {
   const int t = blockIdx.x;
   const WT* row = table + (size_t)tok[t] * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)t * width + c] = to_f<WT>(row[c]);
+  if (!bigram) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)t * width + c] = scale * to_f<WT>(row[c]);
+    return;
+  }
+  long long r = buckets;
+  if (ctl[0] + t > 0) {
+    const long long prev = t > 0 ? tok[t - 1] : carried[0];
+    r = (prev * mul_prev + (long long)tok[t] * mul_cur) % buckets;
+  }
+  const WT* brow = bigram + (size_t)r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)t * width + c] = fmaf(scale, to_f<WT>(row[c]), to_f<WT>(brow[c]));
+}
+// the ring rows of the last taps - 1 positions of a step of T >= taps - 1 tokens (see canon_conv)
+__global__ void canon_history(const float* __restrict__ x, int ld, float* __restrict__ hist, int T, int ch, int taps, const int* __restrict__ ctl) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, back = taps - 1;
+  if (c >= ch) return;
+  for (int j = 0; j < back; j++) {
+    const int tau = T - back + j;
+    hist[(size_t)((ctl[0] + tau) % back) * ch + c] = x[(size_t)tau * ld + c];
+  }
+}
+__global__ void carry_token(const int* __restrict__ tok, int T, int* __restrict__ carried) { carried[0] = tok[T - 1]; }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Causal per-channel convolution in front of a sublayer, added to its input:  u_t = x_t + sum_j w[c][j] x_(t - taps + 1 + j)
+// (the last tap lies on the current token, zeros before the start of the sequence).  `hist` [taps - 1][ch] is a ring over
+// positions: the input of position p lives in row p mod (taps - 1).  Thread = channel, CTA = 128 channels x up to 32 consecutive
+// tokens; rows of earlier steps come from the ring.  A step of at most 32 tokens (one CTA along the tokens) also stores its
+// last taps - 1 inputs in the ring, each thread after its own reads; longer steps run canon_history afterwards, because their
+// first CTA reads the rows that the last one would write (taps - 1 <= 16 is required).
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kCanonTokens = 32, kCanonMaxTaps = 17;
+__global__ void __launch_bounds__(128) canon_conv(const float* __restrict__ x, int ld, const float* __restrict__ w, float* __restrict__ hist,
+                                                  float* __restrict__ u, int ldu, int T, int ch, int taps, const int* __restrict__ ctl) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  const int t0 = blockIdx.y * kCanonTokens, t1 = min(T, t0 + kCanonTokens), pos0 = ctl[0], back = taps - 1;
+  float wk[kCanonMaxTaps], win[kCanonMaxTaps];   // win[j]: the input `back - j` tokens before the current one
+#pragma unroll
+  for (int j = 0; j < kCanonMaxTaps; j++) wk[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+#pragma unroll
+  for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+    float v = 0.f;
+    if (j < back) {
+      const int tau = t0 - back + j;          // token index inside the step (negative: an earlier step)
+      if (tau >= 0) v = x[(size_t)tau * ld + c];
+      else if (pos0 + tau >= 0) v = hist[(size_t)((pos0 + tau) % back) * ch + c];
+    }
+    win[j] = v;
+  }
+  for (int t = t0; t < t1; t++) {
+    const float cur = x[(size_t)t * ld + c];
+    float acc = cur;
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j < back) acc = fmaf(wk[j], win[j], acc);
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps; j++) if (j == back) acc = fmaf(wk[j], cur, acc);
+    u[(size_t)t * ldu + c] = acc;
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 2; j++) if (j + 1 < back) win[j] = win[j + 1];
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j == back - 1) win[j] = cur;
+  }
+  if (gridDim.y == 1 && back > 0) {   // win now holds the inputs of the last `back` positions (older ones first)
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+      if (j < back) {
+        const int p = pos0 + T - back + j;
+        if (p >= 0) hist[(size_t)(p % back) * ch + c] = win[j];
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -130,7 +206,8 @@ __global__ void __launch_bounds__(256) group_rmsnorm(const float* __restrict__ i
 // ---------------------------------------------------------------------------------------------------------------------
 // matrix products
 // ---------------------------------------------------------------------------------------------------------------------
-enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4 };
+enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4, HEPI_GEGLU = 5, HEPI_SIGMUL = 6 };
+__host__ __device__ constexpr bool epi_dual(int epi) { return epi == HEPI_GLU || epi == HEPI_GEGLU; }   // two weight matrices per output
 
 struct GemmP {
   const float* A;          // activations, row pitch lda
@@ -150,6 +227,7 @@ struct GemmP {
   const int* n_tiles;
   float alpha;             // STORE: C = alpha acc; ADD: C += alpha acc
   float lim;               // GLU: g = min(gate, lim), u = clamp(up, -lim, lim), C = g sigmoid(1.702 g) (u + 1)
+                           // GEGLU: C = gelu_tanh(gate) * up;  SIGMUL: C *= sigmoid(acc) (a gate on what C already holds)
   const void* aux;         // GELU_MUL: C = gelu_tanh(acc) * aux[aux_row[row] * aux_ld + aux_off + n]
   const int* aux_row;
   int aux_ld, aux_off;
@@ -163,6 +241,8 @@ __device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict_
   if (EPI == HEPI_STORE) crow[n] = P.alpha * v;
   else if (EPI == HEPI_ADD) crow[n] += P.alpha * v;
   else if (EPI == HEPI_XIELU) crow[n] = v > 0.f ? fmaf(P.act_a * v, v, 0.5f * v) : fmaf(P.act_b, expm1f(v) - v, 0.5f * v);
+  else if (EPI == HEPI_GEGLU) crow[n] = gelu_tanh_f(v) * v2;
+  else if (EPI == HEPI_SIGMUL) crow[n] *= sigmoid_f(v);
   else if (EPI == HEPI_GLU) {
     const float g = fminf(v, P.lim), u = fminf(fmaxf(v2, -P.lim), P.lim);
     crow[n] = g * sigmoid_f(1.702f * g) * (u + 1.f);
@@ -176,7 +256,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict_
 template <typename WT, int EPI>
 __global__ void __launch_bounds__(256) gemm_tiled(const GemmP P) {
   constexpr int BM = 64, BN = 64, BK = 16;
-  constexpr bool DUAL = EPI == HEPI_GLU;
+  constexpr bool DUAL = epi_dual(EPI);
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[DUAL ? 2 : 1][BK][BN + 4];
   __shared__ int rowsA[BM], rowsC[BM];
@@ -296,7 +376,7 @@ template <int EPI>
 __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   typedef __nv_bfloat16 bf;
   constexpr int BM = 128, BT = 128, BK = 32, PITCH = kMmaPitch, ST = kMmaStages;
-  constexpr bool DUAL = EPI == HEPI_GLU;
+  constexpr bool DUAL = epi_dual(EPI);
   constexpr int BN = DUAL ? 64 : 128;
   extern __shared__ __align__(16) unsigned char smraw[];
   bf (*As)[PITCH] = reinterpret_cast<bf (*)[PITCH]>(smraw);                                  // [BM][PITCH]
@@ -464,7 +544,7 @@ template <> struct WVec<__nv_bfloat16> {
 // M <= 4 rows: one warp per weight row, lanes stride over K with 16-byte loads when pitches and bases allow it.
 template <typename WT, int EPI>
 __global__ void __launch_bounds__(256) gemv_rows(const GemmP P) {
-  constexpr bool DUAL = EPI == HEPI_GLU;
+  constexpr bool DUAL = epi_dual(EPI);
   constexpr int MR = 4, V = WVec<WT>::N;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, z = blockIdx.y;
   long long aoff, woff, coff;
@@ -700,6 +780,27 @@ __host__ __device__ __forceinline__ int mask_first(int mask, int size, int i) {
   return i - size + 1 > 0 ? i - size + 1 : 0;
 }
 
+// Row of position j in a cache whose first `keep` rows are fixed (the first positions of a sequence, which a window mask may keep
+// visible for ever) and whose other `ring` rows go round:  keep = 0 is a plain ring.
+__host__ __device__ __forceinline__ long long cache_row(int j, int keep, int ring) { return j < keep ? j : keep + (j - keep) % ring; }
+
+// What the grouped-query attention kernels do to a scaled score before the softmax, and the softmax's extra denominator term:
+//   s <- cap tanh(s / cap) (cap > 0);  s += rel[bucket[min(i - j, rel_max)]][h] (rel non-null; bucket: distance -> row, rel_max + 1 entries);
+//   the denominator also holds e^(sink[h]) (sink non-null).  keep: first positions that stay visible under a window mask.
+struct ScoreMods {
+  float cap;
+  const float* rel;
+  const int* bucket;
+  int rel_max;
+  const float* sink;
+  int keep;
+};
+__device__ __forceinline__ float mod_score(const ScoreMods& sm, float s, int dist, int h, int H) {
+  if (sm.cap > 0.f) s = sm.cap * tanhf(s / sm.cap);
+  if (sm.rel) s += sm.rel[(size_t)sm.bucket[min(dist, sm.rel_max)] * H + h];
+  return s;
+}
+
 template <typename CT, int RV>
 __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__ qa, const CT* __restrict__ cache, float* __restrict__ out,
                                                        int T, int H, int R, const int* __restrict__ ctl, int mask, int window, int ring,
@@ -830,25 +931,36 @@ __global__ void pack_keys_values(const float* __restrict__ kf, const float* __re
   }
 }
 
-// S [H][Tq][Lk] in place: column c is position first + c, row t is position qpos0 + t; entries the mask hides become 0
-__global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int Tq, int Lk, int first, int qpos0, int mask, int window) {
+// S [H][Tq][Lk] in place: the first nk columns are positions 0 .. nk - 1 (kept first positions that lie before `first`), column
+// c >= nk is position first + c - nk; row t is position qpos0 + t and sees j <= i inside its mask or among the kept first
+// positions.  Visible scores are modified (ScoreMods) and normalised, hidden entries become 0.
+__global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int Tq, int Lk, int first, int qpos0, int mask, int window,
+                                                    int nk, ScoreMods sm) {
   __shared__ float red[33];
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x, h = blockIdx.y, H = gridDim.y;
   float* row = S + ((size_t)h * Tq + t) * Lk;
-  const int i = qpos0 + t;
-  const int c_lo = max(0, mask_first(mask, window, i) - first), c_hi = i - first;   // inclusive
+  const int i = qpos0 + t, j_lo = mask_first(mask, window, i);
   float mx = -1e30f;
-  for (int c = c_lo + (int)threadIdx.x; c <= c_hi; c += blockDim.x) mx = fmaxf(mx, row[c]);
+  for (int c = threadIdx.x; c < Lk; c += blockDim.x) {
+    const int j = c < nk ? c : first + c - nk;
+    const bool vis = j <= i && (j >= j_lo || j < sm.keep);
+    const float v = vis ? mod_score(sm, row[c], i - j, h, H) : -1e30f;
+    row[c] = v;
+    mx = fmaxf(mx, v);
+  }
   mx = warp_max(mx);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
   __syncthreads();
   mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  const float sink = sm.sink ? sm.sink[h] : -1e30f;
+  mx = fmaxf(mx, sink);
   float sum = 0.f;
-  for (int c = c_lo + (int)threadIdx.x; c <= c_hi; c += blockDim.x) { const float p = expf(row[c] - mx); row[c] = p; sum += p; }
+  for (int c = threadIdx.x; c < Lk; c += blockDim.x) { const float v = row[c]; const float p = v > -1e29f ? expf(v - mx) : 0.f; row[c] = p; sum += p; }
   sum = block_sum(sum, red);
+  if (sm.sink) sum += expf(sink - mx);
   const float inv = 1.f / sum;
-  for (int c = threadIdx.x; c < Lk; c += blockDim.x) row[c] = (c >= c_lo && c <= c_hi) ? row[c] * inv : 0.f;
+  for (int c = threadIdx.x; c < Lk; c += blockDim.x) row[c] *= inv;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -938,21 +1050,24 @@ __global__ void add_row(float* __restrict__ x, int ld, const float* __restrict__
 //   q <- rot(q / rms(q) * qw),  k <- rot(k / rms(k) * kw)   with the RMS taken over the whole projection (all heads at once);
 //   rot acts on the first rot_dims dimensions of every head: the pair (2i, 2i + 1) turns by the angle pos * freq[i], and cos / sin
 //   are multiplied by `mag`.  Positions and angles are fp32.
-// q goes to q_out; the prepared key goes to row pos % ring of kcache.  Values: with v_src == nullptr the value of a position is
-// the raw output of its key matrix (ahead of the norm and the rotation); otherwise v_src rows (same pitch as k) are cached.
+// q (row pitch ld_q; k: ld_k, v_src: ld_v) goes to q_out; the prepared key goes to row cache_row(pos, keep, ring) of kcache.  Values:
+// with v_src == nullptr the value of a position is the raw output of its key matrix (ahead of the norm and the rotation);
+// otherwise v_src rows are cached, blended with the rows of v_first [T][GV] when that is given: (1 - lam) v + lam v_first.
+// v_keep [T][GV], nullable, receives a copy of what is cached (the rows a later layer blends in).
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q, float* __restrict__ q_out, int HD,
-                                                    const float* __restrict__ k, const float* __restrict__ v_src, int GD, int GV,
+                                                    const float* __restrict__ k, const float* __restrict__ v_src, int GD, int GV, int ld_q, int ld_k, int ld_v,
                                                     const float* __restrict__ qw, const float* __restrict__ kw, float eps, int D,
                                                     int rot_dims, const float* __restrict__ freq, float mag,
                                                     const int* __restrict__ ctl, float* __restrict__ kcache,
-                                                    float* __restrict__ vcache, int ring) {
+                                                    float* __restrict__ vcache, int ring, int keep, const float* __restrict__ v_first,
+                                                    float lam, float* __restrict__ v_keep) {
   __shared__ float red[33];
   const int t = blockIdx.x, pos = ctl[0] + t;
-  const size_t row = (size_t)(pos % ring);
-  const float* qr = q + (size_t)t * HD;
-  const float* kr = k + (size_t)t * GD;
-  const float* vr = v_src ? v_src + (size_t)t * GV : kr;
+  const size_t row = (size_t)cache_row(pos, keep, ring);
+  const float* qr = q + (size_t)t * ld_q;
+  const float* kr = k + (size_t)t * ld_k;
+  const float* vr = v_src ? v_src + (size_t)t * ld_v : kr;
   float sq = 0.f, sk = 0.f;
   for (int e = threadIdx.x; e < HD; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
   for (int e = threadIdx.x; e < GD; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
@@ -978,7 +1093,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q,
     if (isq) q_out[(size_t)t * HD + c] = v;
     else kcache[row * GD + c] = v;
   }
-  for (int e = threadIdx.x; e < GV; e += blockDim.x) vcache[row * GV + e] = vr[e];
+  for (int e = threadIdx.x; e < GV; e += blockDim.x) {
+    float v = vr[e];
+    if (v_first) v = fmaf(lam, v_first[(size_t)t * GV + e], (1.f - lam) * v);
+    vcache[row * GV + e] = v;
+    if (v_keep) v_keep[(size_t)t * GV + e] = v;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -992,12 +1112,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q,
 // in the layout latent_swa_merge reads.
 // ---------------------------------------------------------------------------------------------------------------------
 __host__ __device__ inline size_t gqa_attn_smem_floats(int H, int G, int D, int Dv) {
-  return (size_t)H * D + (size_t)H * 32 + (size_t)32 * (G * D + 1) + 2 * (size_t)H + (size_t)H * Dv + (size_t)H * H + 8 * 32 + 32;
+  return (size_t)H * D + (size_t)H * 32 + (size_t)32 * (G * D + 1) + 2 * (size_t)H + (size_t)H * Dv + (size_t)H * H + 8 * 32 + 32 + 32;
 }
 __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                 float* __restrict__ out, const float* __restrict__ talk, int T, int H, int G, int D,
                                                 int Dv, const int* __restrict__ ctl, int mask, int span, int ring, float scale, int NS,
-                                                float* __restrict__ part) {
+                                                float* __restrict__ part, ScoreMods mods) {
   extern __shared__ float sm[];
   const int GD = G * D, GV = G * Dv, rep = H / G;
   float* qs = sm;                              // [H][D]
@@ -1008,35 +1128,43 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
   float* accs = ls + H;                        // [H][Dv]
   float* tk = accs + (size_t)H * Dv;           // [H][H]
   float* ps = tk + (size_t)H * H;              // [8][32] weights of the warp's current head
-  int* rowoff = reinterpret_cast<int*>(ps + 8 * 32);   // [32] ring rows of the tile's keys
+  int* rowoff = reinterpret_cast<int*>(ps + 8 * 32);   // [32] cache rows of the tile's keys
+  int* kdist = rowoff + 32;                            // [32] their distances from the query
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int t = blockIdx.x, i = ctl[0] + t;
-  int lo = mask_first(mask, span, i), hi = i;
-  if (NS > 1) {   // this CTA's share of the key range (whole tiles of 32)
+  // the visible keys in one index space: the kept first positions that lie before the mask's range, then the range itself
+  const int j_lo = mask_first(mask, span, i), nk = min(mods.keep, j_lo), keep = mods.keep;
+  int lo = 0, hi = nk + i - j_lo;
+  if (NS > 1) {   // this CTA's share of the keys (whole tiles of 32)
     const int tiles = (hi - lo + 32) / 32, per = (tiles + NS - 1) / NS;
     lo += (int)blockIdx.y * per * 32;
     hi = min(hi, lo + per * 32 - 1);
   }
+  auto key_pos = [&](int v) { return v < nk ? v : j_lo + v - nk; };
   for (int e = tid; e < H * D; e += blockDim.x) qs[e] = q[(size_t)t * H * D + e];
   for (int e = tid; e < H; e += blockDim.x) { ms[e] = -1e30f; ls[e] = 0.f; }
   for (int e = tid; e < H * Dv; e += blockDim.x) accs[e] = 0.f;
   if (talk) for (int e = tid; e < H * H; e += blockDim.x) tk[e] = talk[e];
   for (int j0 = lo; j0 <= hi; j0 += 32) {
     __syncthreads();
-    if (tid < 32) rowoff[tid] = (j0 + tid) % ring;
+    if (tid < 32) {   // keys past the share's end get weight 0 below and any initialised row
+      const int p = key_pos(min(j0 + tid, hi));
+      rowoff[tid] = (int)cache_row(p, keep, ring);
+      kdist[tid] = i - p;
+    }
     if ((GD & 3) == 0) {   // 16-byte loads, several in flight per thread (the rows are 16-byte aligned: GD * 4 bytes each)
       const int GD4 = GD >> 2;
 #pragma unroll 8
       for (int e = tid; e < 32 * GD4; e += 256) {
         const int jj = e / GD4, r = (e - jj * GD4) * 4, j = j0 + jj;
-        const float4 v = j <= hi ? *reinterpret_cast<const float4*>(kc + (size_t)(j % ring) * GD + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 v = j <= hi ? *reinterpret_cast<const float4*>(kc + (size_t)cache_row(key_pos(j), keep, ring) * GD + r) : make_float4(0.f, 0.f, 0.f, 0.f);
         float* d = ks + jj * (GD + 1) + r;
         d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
       }
     } else {
       for (int e = tid; e < 32 * GD; e += blockDim.x) {
         const int jj = e / GD, r = e - jj * GD, j = j0 + jj;
-        ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)(j % ring) * GD + r] : 0.f;
+        ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)cache_row(key_pos(j), keep, ring) * GD + r] : 0.f;
       }
     }
     __syncthreads();
@@ -1060,7 +1188,7 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
         s = 0.f;
         for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * 32 + lane], s);
       } else s = sc[h * 32 + lane];
-      s = valid ? s : -1e30f;
+      s = valid ? mod_score(mods, s, kdist[lane], h, H) : -1e30f;
       const float m_old = ms[h];
       const float m_new = fmaxf(m_old, warp_max(s));
       const float corr = expf(m_old - m_new);
@@ -1101,12 +1229,19 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
   }
   __syncthreads();
   for (int h = w; h < H; h += 8) {
+    float m = ms[h], l = ls[h], corr = 1.f;
+    if (mods.sink && blockIdx.y == 0) {   // the sink joins the first share like a key with a zero value vector
+      const float sk = mods.sink[h], m_new = fmaxf(m, sk);
+      corr = expf(m - m_new);
+      l = l * corr + expf(sk - m_new);
+      m = m_new;
+    }
     if (NS > 1) {
       float* pp = part + (((size_t)t * H + h) * NS + blockIdx.y) * (Dv + 2);
-      if (lane == 0) { pp[0] = ms[h]; pp[1] = ls[h]; }
-      for (int r = lane; r < Dv; r += 32) pp[2 + r] = accs[h * Dv + r];
+      if (lane == 0) { pp[0] = m; pp[1] = l; }
+      for (int r = lane; r < Dv; r += 32) pp[2 + r] = accs[h * Dv + r] * corr;
     } else {
-      const float inv = 1.f / ls[h];
+      const float inv = corr / l;
       for (int r = lane; r < Dv; r += 32) out[((size_t)t * H + h) * Dv + r] = accs[h * Dv + r] * inv;
     }
   }
@@ -1115,11 +1250,12 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
 // Portions run the same attention as matrix products per block of queries (like the latent attention above).  pack_ring_kv
 // gathers the visible positions first .. first + Lk - 1 from the ring caches into per-group operands: keys [G][Lk][D], values
 // transposed [G][Dv][Lk].  mix_heads applies the heads' score mixing to a [H][Tq][Lk] score array (out of place).
+// The first nk operand rows are the kept first positions 0 .. nk - 1 (cache rows of their own, see cache_row).
 template <typename WT>
 __global__ void pack_ring_kv(const float* __restrict__ kc, const float* __restrict__ vc, WT* __restrict__ kb, WT* __restrict__ vt,
-                             int first, int Lk, int ring, int G, int D, int Dv) {
+                             int first, int Lk, int ring, int G, int D, int Dv, int nk, int keep) {
   const int j = blockIdx.x;
-  const size_t row = (size_t)((first + j) % ring);
+  const size_t row = (size_t)cache_row(j < nk ? j : first + j - nk, keep, ring);
   for (int e = threadIdx.x; e < G * D; e += blockDim.x) {
     const int g = e / D, d = e - g * D;
     kb[((size_t)g * Lk + j) * D + d] = from_f<WT>(kc[row * G * D + e]);
@@ -1127,6 +1263,69 @@ __global__ void pack_ring_kv(const float* __restrict__ kc, const float* __restri
   for (int e = threadIdx.x; e < G * Dv; e += blockDim.x) {
     const int g = e / Dv, v = e - g * Dv;
     vt[((size_t)g * Dv + v) * Lk + j] = from_f<WT>(vc[row * G * Dv + e]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Latent attention with a rotated key part (DSK_MIX_MLA), one CTA per token of the step (position ctl[0] + t):
+//   cache row cache_row(pos, 0, ring) <- [ rms(dkv[0:R]) * w  |  rot(dkv[R:R+Rd], pos) ]      (dkv: row pitch ld_dkv)
+//   q [T][H][D + Rd]: the last Rd entries of every head are rotated in place;  qa_rot (nullable) [T][H][R + Rd]: the rotated
+//   part is also copied behind the R entries that the absorbed key up-projection fills (decode-sized steps score
+//   [W_uk^T q_plain | q_rot] against the cache rows directly).
+// rot turns the pairs (2i, 2i + 1), i < rot_dims / 2, by pos * freq[i]; positions and angles are fp32.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) mla_prepare(const float* __restrict__ dkv, int ld_dkv, const float* __restrict__ w, float eps,
+                                                   float* __restrict__ q, float* __restrict__ qa_rot, int H, int D, int Rd, int R,
+                                                   int rot_dims, const float* __restrict__ freq, const int* __restrict__ ctl,
+                                                   float* __restrict__ cache, int ring) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, pos = ctl[0] + t, RW = R + Rd;
+  const float* src = dkv + (size_t)t * ld_dkv;
+  float* crow = cache + (size_t)cache_row(pos, 0, ring) * RW;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < R; e += blockDim.x) ss = fmaf(src[e], src[e], ss);
+  const float sc = 1.f / sqrtf(block_sum(ss, red) / (float)R + eps);
+  for (int e = threadIdx.x; e < R; e += blockDim.x) crow[e] = src[e] * sc * w[e];
+  const float fpos = (float)pos;
+  const int half = rot_dims >> 1;
+  // pairs of the shared key part (head index H) and of every query head
+  for (int e = threadIdx.x; e < (H + 1) * half; e += blockDim.x) {
+    const int h = e / half, i = e - h * half;
+    float sn, cs;
+    sincosf(fpos * freq[i], &sn, &cs);
+    if (h == H) {
+      const float a = src[R + 2 * i], b = src[R + 2 * i + 1];
+      crow[R + 2 * i] = a * cs - b * sn;
+      crow[R + 2 * i + 1] = b * cs + a * sn;
+    } else {
+      float* qr = q + ((size_t)t * H + h) * (D + Rd) + D;
+      const float a = qr[2 * i], b = qr[2 * i + 1];
+      const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+      qr[2 * i] = ra; qr[2 * i + 1] = rb;
+      if (qa_rot) { float* o = qa_rot + ((size_t)t * H + h) * RW + R; o[2 * i] = ra; o[2 * i + 1] = rb; }
+    }
+  }
+  for (int e = threadIdx.x; e < (H + 1) * (Rd - rot_dims); e += blockDim.x) {   // entries that pass unchanged
+    const int h = e / (Rd - rot_dims), d = rot_dims + e - h * (Rd - rot_dims);
+    if (h == H) crow[R + d] = src[R + d];
+    else if (qa_rot) qa_rot[((size_t)t * H + h) * RW + R + d] = q[((size_t)t * H + h) * (D + Rd) + D + d];
+  }
+}
+
+// Portions: per-head operands of the score and value products from the up-projected plain keys kf [Lk][H*D], values vf
+// [Lk][H*V] and the rotated key parts of the cache rows rows[j] ([R + Rd] each):  kb [H][Lk][D + Rd], vt [H][V][Lk].
+__global__ void pack_mla_kv(const float* __restrict__ kf, const float* __restrict__ vf, const float* __restrict__ cache,
+                            const int* __restrict__ rows, float* __restrict__ kb, float* __restrict__ vt, int Lk, int H, int D, int Rd,
+                            int R, int V) {
+  const int j = blockIdx.x, DK = D + Rd;
+  const float* kr = cache + (size_t)rows[j] * (R + Rd) + R;
+  for (int e = threadIdx.x; e < H * DK; e += blockDim.x) {
+    const int h = e / DK, d = e - h * DK;
+    kb[((size_t)h * Lk + j) * DK + d] = d < D ? kf[(size_t)j * H * D + h * D + d] : kr[d - D];
+  }
+  for (int e = threadIdx.x; e < H * V; e += blockDim.x) {
+    const int h = e / V, v = e - h * V;
+    vt[((size_t)h * V + v) * Lk + j] = vf[(size_t)j * H * V + e];
   }
 }
 

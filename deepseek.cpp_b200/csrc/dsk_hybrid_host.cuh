@@ -12,6 +12,9 @@
 //   mlp.router, mlp.correction, mlp.e<j>.gate|up|down                                                 (routed feed-forward)
 //   mlp.up, mlp.up.b, mlp.down, mlp.down.b, mlp.act                                                   (dense feed-forward)
 //   side.gate, side.proj, side.norm                                                                   (per-layer token input)
+// Grouped-query attention with its switches on adds mix.v, mix.q.b / k.b / v.b, mix.rel, mix.sink, mix.vmix; latent attention with a
+// rotated key part (DSK_MIX_MLA) has mix.dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o; a gated dense feed-forward mlp.gate / up / down;
+// DSK_BLOCK_POST layers norm1 / norm2, ls1 / ls2, canon1 / canon2, rg1 / rg2 (+ .b); the model "bigram" beside "embed".
 // A parallel block computes, with h = norm1(x):  x += m (mixer(h) + ff(h));  a sandwich block  x += norm1b(mixer(norm1(x))),
 // x += norm2b(ff(norm2(x))).  Then, when the model has a per-layer token table,
 // g = gelu_tanh(side.gate x) * side.embed[token][i*sd : (i+1)*sd],  y = side.proj g,  x += m * rmsnorm(y) * side.norm.
@@ -44,8 +47,24 @@ struct HLayer {
   HTensor kproj;
   float *q_norm = nullptr, *k_norm = nullptr, *talk = nullptr, *rot_freq = nullptr;
   float rot_mag = 1.f;
-  // dense feed-forward
-  HTensor up, down;
+  // grouped-query attention with a value matrix: q, k and v rows stacked into one matrix (one product per step) with their biases
+  HTensor qkv;
+  float *qkv_b = nullptr, *rel = nullptr, *sink = nullptr;
+  int* rel_bucket = nullptr;        // distance (0 .. att_rel_max) -> row of rel
+  int rel_rows = 0;
+  float vmix = 0.f;                 // value-mixing weight (mix.vmix), read once at upload
+  char have_qkv[3] = {0, 0, 0}, have_qkvb[3] = {0, 0, 0}, have_vmix = 0;
+  // latent attention with a rotated key part: the two down-projections stacked [q_rank | kv_rank + rot_dim], query up-projection, output gate
+  HTensor in2, uq, gmat;
+  float* dq_norm = nullptr;
+  char have_in2[2] = {0, 0};
+  // DSK_BLOCK_POST: input convolutions, residual gates, closing norm weights (norm weight x layer scale, folded when the model is finalised)
+  HTensor rg1, rg2;
+  float *rg1_b = nullptr, *rg2_b = nullptr, *canon1 = nullptr, *canon2 = nullptr, *ls1 = nullptr, *ls2 = nullptr, *close1 = nullptr, *close2 = nullptr;
+  float norm1_s = 1.f, norm2_s = 1.f;   // single-number norm weights
+  char have_n1 = 0, have_n2 = 0;
+  // dense feed-forward (gate_d: the gate matrix of a gated one)
+  HTensor up, down, gate_d;
   float *up_b = nullptr, *down_b = nullptr, *act = nullptr;
   float act_a = 0.f, act_b = 0.f;
   // routed feed-forward
@@ -68,8 +87,9 @@ struct Model {
   dsk_hybrid_config c;
   std::vector<HLayer> L;
   std::vector<Run> runs;
-  HTensor embed, side_embed, head;
+  HTensor embed, side_embed, head, bigram;
   float *final_norm = nullptr, *loop_step = nullptr;
+  int vmix_first = -1;              // the first layer whose values later value-mixing layers blend in
   size_t wsize = 4;                 // bytes per matrix element
 };
 
@@ -78,7 +98,8 @@ struct LayerState {
   float* hist = nullptr;            // [conv - 1][channels]
   void* cache = nullptr;            // [ring][kv_rank] (owner layers); grouped-query attention: keys [ring][kv_heads * dim]
   void* vcache = nullptr;           // grouped-query attention: values [ring][kv_heads * vdim]
-  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0, vcache_bytes = 0;
+  float* canon = nullptr;           // DSK_BLOCK_POST: [2][taps - 1][width] rings of the two input convolutions
+  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0, vcache_bytes = 0, canon_bytes = 0;
 };
 
 struct State {
@@ -95,7 +116,9 @@ struct State {
   void *kb = nullptr, *vt = nullptr;
   int* d_rows = nullptr;
   int prefill_keys = 0;                      // keys a block of queries can see at most; 0: the matrix path is off
-  float* y = nullptr;                        // a sublayer's output before its closing norm (sandwich blocks)
+  float* y = nullptr;                        // a sublayer's output before its closing norm (sandwich and post blocks)
+  float* vfirst = nullptr;                   // [chunk][kv_heads * vdim] values of the step's tokens in the first value-mixing layer
+  int* d_prev = nullptr;                     // the sequence's last token (bigram embedding)
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
   int *h_tok = nullptr, *h_want = nullptr;   // pinned staging of a chunk's token ids / wanted rows
   std::vector<void*> allocs;
@@ -122,7 +145,13 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
   if (c.norm_groups <= 0 || c.dim % c.norm_groups != 0) return fail(-1, "norm groups %d do not divide width %d", c.norm_groups, c.dim);
   if (c.chunk < 1 || c.chunk > 4096) return fail(-1, "chunk %d out of range (1..4096)", c.chunk);
   if (c.side_dim < 0) return fail(-1, "negative side_dim");
-  if (c.block != DSK_BLOCK_PARALLEL && c.block != DSK_BLOCK_SANDWICH) return fail(-1, "unknown block kind %d", c.block);
+  if (c.block != DSK_BLOCK_PARALLEL && c.block != DSK_BLOCK_SANDWICH && c.block != DSK_BLOCK_POST) return fail(-1, "unknown block kind %d", c.block);
+  if (c.block == DSK_BLOCK_POST && (c.norm_kind != DSK_NORM_RMS || c.norm_groups != 1 || c.side_dim > 0 || c.loop_times >= 1))
+    return fail(-1, "post-norm blocks run with plain RMS norms, without a per-layer token input and without a layer loop");
+  if (c.block != DSK_BLOCK_POST && (c.canon_taps || c.res_gate || c.layer_scale || c.norm_scalar))
+    return fail(-1, "input convolutions, gated residuals, layer scales and single-number norm weights belong to post-norm blocks");
+  if (c.canon_taps < 0 || c.canon_taps > kCanonMaxTaps) return fail(-1, "input convolution of %d taps unsupported (at most %d)", c.canon_taps, kCanonMaxTaps);
+  if (c.bigram_buckets < 0) return fail(-1, "negative bigram table size");
   if (c.norm_kind != DSK_NORM_RMS && c.norm_kind != DSK_NORM_LAYER) return fail(-1, "unknown norm kind %d", c.norm_kind);
   if (c.loop_times >= 1 && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop))
     return fail(-1, "layer loop %d..%d outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
@@ -146,16 +175,26 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
     } else if (s.mixer == DSK_MIX_GQA) {
       if (s.att_heads <= 0 || s.att_kv_heads <= 0 || s.att_dim <= 0 || s.att_vdim <= 0 || s.att_window <= 0) return fail(-1, "layer %d: bad attention sizes", i);
       if (s.att_heads % s.att_kv_heads != 0) return fail(-1, "layer %d: heads %d not a multiple of kv_heads %d", i, s.att_heads, s.att_kv_heads);
-      if (s.att_vdim != s.att_dim) return fail(-1, "layer %d: values come out of the key matrix, so vdim %d must equal dim %d", i, s.att_vdim, s.att_dim);
+      if (!s.att_value_proj && s.att_vdim != s.att_dim) return fail(-1, "layer %d: values come out of the key matrix, so vdim %d must equal dim %d", i, s.att_vdim, s.att_dim);
+      if (s.att_bias && !s.att_value_proj) return fail(-1, "layer %d: projection biases need the stacked q / k / v projection (att_value_proj)", i);
+      if (s.att_talk && (s.att_softcap > 0.f || s.att_rel_max > 0)) return fail(-1, "layer %d: head mixing together with a score cap or distance bias is undefined", i);
+      if (s.att_keep_first < 0 || (s.att_keep_first > 0 && s.att_mask != DSK_MASK_WINDOW)) return fail(-1, "layer %d: kept first positions belong to a window mask", i);
+      if (s.att_rel_max < 0 || s.att_softcap < 0.f) return fail(-1, "layer %d: negative score cap or distance limit", i);
       if (s.rot_dims < 0 || s.rot_dims > s.att_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most dim %d", i, s.rot_dims, s.att_dim);
       if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
       if (gqa_attn_smem_floats(s.att_heads, s.att_kv_heads, s.att_dim, s.att_vdim) * 4 > 200 * 1024)
         return fail(-1, "layer %d: %d heads x %d with %d key heads do not fit the attention kernel's shared memory", i, s.att_heads, s.att_dim, s.att_kv_heads);
+    } else if (s.mixer == DSK_MIX_MLA) {
+      if (s.att_heads <= 0 || s.att_dim <= 0 || s.att_rot_dim < 0 || s.att_vdim <= 0 || s.att_kv_rank <= 0 || s.att_q_rank <= 0 || s.att_window <= 0)
+        return fail(-1, "layer %d: bad latent-attention sizes", i);
+      if (s.att_kv_rank + s.att_rot_dim > 1024) return fail(-1, "layer %d: kv_rank + rot_dim %d > 1024 unsupported", i, s.att_kv_rank + s.att_rot_dim);
+      if (s.rot_dims < 0 || s.rot_dims > s.att_rot_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most rot_dim %d", i, s.rot_dims, s.att_rot_dim);
+      if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
     } else return fail(-1, "layer %d: unknown mixer %d", i, s.mixer);
     if (s.mixer != DSK_MIX_SSD && s.att_mask != DSK_MASK_WINDOW && s.att_mask != DSK_MASK_CHUNK) return fail(-1, "layer %d: unknown mask %d", i, s.att_mask);
     if (s.ff_kind == DSK_FF_DENSE) {
       if (s.ff_hidden <= 0) return fail(-1, "layer %d: bad feed-forward size", i);
-      if (s.ff_act != DSK_ACT_XIELU) return fail(-1, "layer %d: unknown activation %d", i, s.ff_act);
+      if (s.ff_act != DSK_ACT_XIELU && s.ff_act != DSK_ACT_GEGLU) return fail(-1, "layer %d: unknown activation %d", i, s.ff_act);
     } else if (s.ff_kind == DSK_FF_MOE) {
       if (s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || s.ff_hidden <= 0) return fail(-1, "layer %d: bad routed feed-forward sizes", i);
       if (s.ff_experts > 4096) return fail(-1, "layer %d: more than 4096 experts unsupported", i);
@@ -180,6 +219,8 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_mma<HEPI_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_GELU_MUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_XIELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_SIGMUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gqa_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(mix_heads, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
@@ -205,7 +246,13 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
     L.sp = layers[i];
     if (L.sp.ff_kind == DSK_FF_MOE) L.have.assign(3 * (size_t)L.sp.ff_experts, 0);
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) L.owner = L.sp.att_kv_from >= 0 ? L.sp.att_kv_from : i;
-    if (L.sp.mixer == DSK_MIX_GQA) L.owner = i;
+    if (L.sp.mixer == DSK_MIX_GQA || L.sp.mixer == DSK_MIX_MLA) L.owner = i;
+    if (L.sp.mixer == DSK_MIX_GQA && L.sp.att_vmix) {
+      if (M->vmix_first < 0) M->vmix_first = i;
+      else if ((long long)L.sp.att_kv_heads * L.sp.att_vdim != (long long)M->L[M->vmix_first].sp.att_kv_heads * M->L[M->vmix_first].sp.att_vdim) {
+        fail(-1, "layer %d: value mixing needs as many value entries per token as layer %d has", i, M->vmix_first); dsk_model_destroy(m); return nullptr;
+      }
+    }
   }
   // ring caches: the owner keeps the widest window (or chunk of the mask) among its readers plus one step, capped by the sequence limit
   for (int i = 0; i < cfg->n_layers; i++) {
@@ -229,11 +276,11 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
       if (M->runs[q].layer == o) { M->runs[r].owner_run = q; break; }
     if (M->runs[r].owner_run < 0) { fail(-1, "layer %d reads the latent cache of layer %d, which has not run before it", M->runs[r].layer, o); dsk_model_destroy(m); return nullptr; }
   }
-  // rotation tables of the grouped-query attention layers: frequency per pair, in double, rounded once to fp32
+  // rotation tables of the attention layers that rotate: frequency per pair, in double, rounded once to fp32
   for (int i = 0; i < cfg->n_layers; i++) {
     HLayer& L = M->L[i];
     const dsk_layer_spec& s = L.sp;
-    if (s.mixer != DSK_MIX_GQA || s.rot_dims <= 0) continue;
+    if ((s.mixer != DSK_MIX_GQA && s.mixer != DSK_MIX_MLA) || s.rot_dims <= 0) continue;
     const int half = s.rot_dims / 2;
     std::vector<float> f((size_t)half);
     const double base = s.rot_base, dims = s.rot_dims;
@@ -312,7 +359,47 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
     if (dmalloc(m, (void**)dst, (size_t)rows * std::max<long long>(cols, 1) * 4)) return -2;
     return put(name, dtype, shape, data, nbytes, on_dev, rows, cols, *dst, false, 0);
   };
+  // rows [row0, row0 + rows) of a matrix that stacks several checkpoint tensors (one product instead of several per step)
+  auto STACK = [&](HTensor& st, long long total, long long cols, long long row0, long long rows, char* have) -> int {
+    if (*have) return fail(-4, "tensor %s uploaded twice", name);
+    if (!st.p) {
+      if (dmalloc(m, &st.p, (size_t)total * cols * M->wsize + 16)) return -2;
+      st.rows = total; st.cols = cols;
+    }
+    *have = 1;
+    return put(name, dtype, shape, data, nbytes, on_dev, rows, cols, (char*)st.p + (size_t)row0 * cols * M->wsize, bf, 0);
+  };
+  auto STACKV = [&](float** dst, long long total, long long off, long long n, char* have) -> int {   // the same for fp32 vectors
+    if (*have) return fail(-4, "tensor %s uploaded twice", name);
+    if (!*dst) { if (dmalloc(m, (void**)dst, (size_t)total * 4)) return -2; }
+    *have = 1;
+    return put(name, dtype, shape, data, nbytes, on_dev, n, 0, *dst + off, false, 0);
+  };
+  // a single number (shape []) -> host float
+  auto SCALAR = [&](float* dst, char* have) -> int {
+    if (*have) return fail(-4, "tensor %s uploaded twice", name);
+    if (dtype != DSK_DT_BF16 && dtype != DSK_DT_F32) return fail(-4, "tensor %s: dtype %s unsupported (BF16 or F32)", name, dtype_name(dtype));
+    const size_t es = dtype == DSK_DT_BF16 ? 2 : 4;
+    if (shape[0] > 1 || shape[1] != 0 || nbytes != es) return fail(-4, "tensor mismatch for %s: expected a single number, got shape=[%lld,%lld] (%zu bytes)", name, (long long)shape[0], (long long)shape[1], nbytes);
+    unsigned char raw[4] = {0, 0, 0, 0};
+    if (on_dev) CK(cudaMemcpy(raw, data, es, cudaMemcpyDeviceToHost)); else memcpy(raw, data, es);
+    uint32_t bits;
+    if (es == 2) bits = ((uint32_t)raw[0] | ((uint32_t)raw[1] << 8)) << 16; else memcpy(&bits, raw, 4);
+    memcpy(dst, &bits, 4);
+    *have = 1;
+    return 0;
+  };
   if (nm == "embed") return MAT(M->embed, c.vocab_size, c.dim);
+  if (nm == "bigram" && c.bigram_buckets > 0) return MAT(M->bigram, (long long)c.bigram_buckets + 1, c.dim);
+  if (nm == "final.norm" && c.norm_scalar) {   // one number for all coordinates: kept as a constant vector, so every norm kernel takes it
+    if (M->final_norm) return fail(-4, "tensor %s uploaded twice", name);
+    float g = 0.f; char have = 0;
+    if (int rc = SCALAR(&g, &have)) return rc;
+    std::vector<float> v((size_t)c.dim, g);
+    if (dmalloc(m, (void**)&M->final_norm, (size_t)c.dim * 4)) return -2;
+    CK(cudaMemcpy(M->final_norm, v.data(), (size_t)c.dim * 4, cudaMemcpyHostToDevice));
+    return 0;
+  }
   if (nm == "final.norm") return F32(&M->final_norm, c.dim, 0);
   if (nm == "head") {
     if (c.tie_head) return fail(-4, "tensor %s: this model's LM head is its embedding table", name);
@@ -333,7 +420,25 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
   HLayer& L = M->L[li];
   const dsk_layer_spec& s = L.sp;
   const std::string rest(end + 1);
-  if (rest == "norm1") return F32(&L.norm1, c.dim, 0);
+  if (c.block == DSK_BLOCK_POST) {
+    const bool ff = s.ff_kind != DSK_FF_NONE;
+    if (rest == "norm1") return c.norm_scalar ? SCALAR(&L.norm1_s, &L.have_n1) : F32(&L.norm1, c.dim, 0);
+    if (rest == "norm2" && ff) return c.norm_scalar ? SCALAR(&L.norm2_s, &L.have_n2) : F32(&L.norm2, c.dim, 0);
+    if (c.layer_scale) {
+      if (rest == "ls1") return F32(&L.ls1, c.dim, 0);
+      if (rest == "ls2" && ff) return F32(&L.ls2, c.dim, 0);
+    }
+    if (c.canon_taps > 0) {
+      if (rest == "canon1") return F32(&L.canon1, c.dim, c.canon_taps);
+      if (rest == "canon2" && ff) return F32(&L.canon2, c.dim, c.canon_taps);
+    }
+    if (c.res_gate) {
+      if (rest == "rg1") return MAT(L.rg1, c.dim, c.dim);
+      if (rest == "rg1.b") return F32(&L.rg1_b, c.dim, 0);
+      if (rest == "rg2" && ff) return MAT(L.rg2, c.dim, c.dim);
+      if (rest == "rg2.b" && ff) return F32(&L.rg2_b, c.dim, 0);
+    }
+  } else if (rest == "norm1") return F32(&L.norm1, c.dim, 0);
   if (c.block == DSK_BLOCK_SANDWICH) {
     if (rest == "norm1b") return F32(&L.norm1b, c.dim, 0);
     if (rest == "norm2" && s.ff_kind != DSK_FF_NONE) return F32(&L.norm2, c.dim, 0);
@@ -351,10 +456,39 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "D") return F32(&L.D, s.ssm_heads, 0);
       if (k == "norm") return F32(&L.mnorm, inner, 0);
       if (k == "o") return MAT(L.o, c.dim, inner);
+    } else if (s.mixer == DSK_MIX_MLA) {
+      const long long H = s.att_heads, DK = s.att_dim + s.att_rot_dim, R = s.att_kv_rank, Q = s.att_q_rank, tot = Q + R + s.att_rot_dim;
+      if (k == "dq") return STACK(L.in2, tot, c.dim, 0, Q, &L.have_in2[0]);
+      if (k == "dkv") return STACK(L.in2, tot, c.dim, Q, R + s.att_rot_dim, &L.have_in2[1]);
+      if (k == "dq.norm") return F32(&L.dq_norm, Q, 0);
+      if (k == "dkv.norm") return F32(&L.dkv_norm, R, 0);
+      if (k == "uq") return MAT(L.uq, H * DK, Q);
+      if (k == "uk") { if (int rc = MAT(L.ukT, H * s.att_dim, R, s.att_dim)) return rc; return MAT(L.uk, H * s.att_dim, R); }
+      if (k == "uv") return MAT(L.uv, H * s.att_vdim, R);
+      if (k == "g" && s.att_out_gate) return MAT(L.gmat, H * s.att_vdim, c.dim);
+      if (k == "o") return MAT(L.o, c.dim, H * s.att_vdim);
     } else if (s.mixer == DSK_MIX_GQA) {
-      const long long HD = (long long)s.att_heads * s.att_dim, GD = (long long)s.att_kv_heads * s.att_dim;
-      if (k == "q") return MAT(L.q, HD, c.dim);
-      if (k == "k") return MAT(L.kproj, GD, c.dim);
+      const long long HD = (long long)s.att_heads * s.att_dim, GD = (long long)s.att_kv_heads * s.att_dim, GV = (long long)s.att_kv_heads * s.att_vdim;
+      if (s.att_value_proj) {
+        const long long tot = HD + GD + GV;
+        if (k == "q") return STACK(L.qkv, tot, c.dim, 0, HD, &L.have_qkv[0]);
+        if (k == "k") return STACK(L.qkv, tot, c.dim, HD, GD, &L.have_qkv[1]);
+        if (k == "v") return STACK(L.qkv, tot, c.dim, HD + GD, GV, &L.have_qkv[2]);
+        if (s.att_bias) {
+          if (k == "q.b") return STACKV(&L.qkv_b, tot, 0, HD, &L.have_qkvb[0]);
+          if (k == "k.b") return STACKV(&L.qkv_b, tot, HD, GD, &L.have_qkvb[1]);
+          if (k == "v.b") return STACKV(&L.qkv_b, tot, HD + GD, GV, &L.have_qkvb[2]);
+        }
+      }
+      if (k == "rel" && s.att_rel_max > 0) {   // the number of distance buckets is the tensor's first size
+        if (shape[0] < 2 || shape[0] > (1 << 20)) return fail(-4, "tensor %s: %lld distance buckets", name, (long long)shape[0]);
+        L.rel_rows = (int)shape[0];
+        return F32(&L.rel, shape[0], s.att_heads);
+      }
+      if (k == "sink" && s.att_sink) return F32(&L.sink, s.att_heads, 0);
+      if (k == "vmix" && s.att_vmix) return SCALAR(&L.vmix, &L.have_vmix);
+      if (k == "q" && !s.att_value_proj) return MAT(L.q, HD, c.dim);
+      if (k == "k" && !s.att_value_proj) return MAT(L.kproj, GD, c.dim);
       if (k == "q.norm") return F32(&L.q_norm, HD, 0);
       if (k == "k.norm") return F32(&L.k_norm, GD, 0);
       if (k == "talk" && s.att_talk) return F32(&L.talk, s.att_heads, s.att_heads);
@@ -371,6 +505,13 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       }
     }
     return fail(-4, "unknown tensor name %s for this layer's mixer", name);
+  }
+  if (rest.rfind("mlp.", 0) == 0 && s.ff_kind == DSK_FF_DENSE && s.ff_act == DSK_ACT_GEGLU) {
+    const std::string k = rest.substr(4);
+    if (k == "gate") return MAT(L.gate_d, s.ff_hidden, c.dim);
+    if (k == "up") return MAT(L.up, s.ff_hidden, c.dim);
+    if (k == "down") return MAT(L.down, c.dim, s.ff_hidden);
+    return fail(-4, "unknown tensor name %s", name);
   }
   if (rest.rfind("mlp.", 0) == 0 && s.ff_kind == DSK_FF_DENSE) {
     const std::string k = rest.substr(4);
@@ -430,16 +571,54 @@ static int finalize(dsk_model* m) {
   if (!M->final_norm) return fail(-5, "missing tensor final.norm");
   if (c.side_dim > 0 && !M->side_embed.present) return fail(-5, "missing tensor side.embed");
   if (!c.tie_head && !M->head.present) return fail(-5, "missing tensor head");
+  if (c.bigram_buckets > 0 && !M->bigram.present) return fail(-5, "missing tensor bigram");
+  // closing norm weight of a post-norm sublayer: (norm weight, a vector or one number) x (layer scale), folded once in fp32
+  auto fold = [&](const float* normv, float norm_s, const float* ls, float** out) -> int {
+    std::vector<float> a((size_t)c.dim, norm_s), b((size_t)c.dim, 1.f);
+    if (normv) CK(cudaMemcpy(a.data(), normv, (size_t)c.dim * 4, cudaMemcpyDeviceToHost));
+    if (ls) CK(cudaMemcpy(b.data(), ls, (size_t)c.dim * 4, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < c.dim; i++) a[i] *= b[i];
+    if (!*out && dmalloc(m, (void**)out, (size_t)c.dim * 4)) return -2;
+    CK(cudaMemcpy(*out, a.data(), (size_t)c.dim * 4, cudaMemcpyHostToDevice));
+    return 0;
+  };
+  CK(cudaDeviceSynchronize());
   if (c.loop_times >= 1 && c.loop_stop > c.loop_start && !M->loop_step) return fail(-5, "missing tensor loop.step");
   for (int i = 0; i < c.n_layers; i++) {
     HLayer& L = M->L[i];
     const dsk_layer_spec& s = L.sp;
-    if (!L.norm1) return fail(-5, "missing tensor l%d.norm1", i);
+    if (c.block == DSK_BLOCK_POST) {
+      const bool ff = s.ff_kind != DSK_FF_NONE;
+      if (c.norm_scalar ? (!L.have_n1 || (ff && !L.have_n2)) : (!L.norm1 || (ff && !L.norm2))) return fail(-5, "layer %d: missing norm tensors (norm1, norm2)", i);
+      if (c.layer_scale && (!L.ls1 || (ff && !L.ls2))) return fail(-5, "layer %d: missing layer scale tensors (ls1, ls2)", i);
+      if (c.canon_taps > 0 && (!L.canon1 || (ff && !L.canon2))) return fail(-5, "layer %d: missing input convolution tensors (canon1, canon2)", i);
+      if (c.res_gate && (!L.rg1.present || !L.rg1_b || (ff && (!L.rg2.present || !L.rg2_b)))) return fail(-5, "layer %d: missing residual gate tensors (rg1, rg1.b, rg2, rg2.b)", i);
+      if (fold(L.norm1, L.norm1_s, L.ls1, &L.close1) || (ff && fold(L.norm2, L.norm2_s, L.ls2, &L.close2))) return -2;
+    } else if (!L.norm1) return fail(-5, "missing tensor l%d.norm1", i);
     if (c.block == DSK_BLOCK_SANDWICH && (!L.norm1b || (s.ff_kind != DSK_FF_NONE && (!L.norm2 || !L.norm2b))))
       return fail(-5, "layer %d: missing norm tensors (norm1b, norm2, norm2b)", i);
     if (s.mixer == DSK_MIX_GQA) {
-      if (!L.q.present || !L.kproj.present || !L.o.present || !L.q_norm || !L.k_norm || (s.att_talk && !L.talk))
-        return fail(-5, "layer %d: missing attention tensors (mix.q, k, q.norm, k.norm, talk, o)", i);
+      if (s.att_value_proj) {
+        L.qkv.present = L.have_qkv[0] && L.have_qkv[1] && L.have_qkv[2];
+        if (!L.qkv.present || (s.att_bias && !(L.have_qkvb[0] && L.have_qkvb[1] && L.have_qkvb[2]))) return fail(-5, "layer %d: missing attention projections (mix.q, k, v and their biases)", i);
+      } else if (!L.q.present || !L.kproj.present) return fail(-5, "layer %d: missing attention tensors (mix.q, k)", i);
+      if (!L.o.present || !L.q_norm || !L.k_norm || (s.att_talk && !L.talk))
+        return fail(-5, "layer %d: missing attention tensors (mix.q.norm, k.norm, talk, o)", i);
+      if ((s.att_sink && !L.sink) || (s.att_rel_max > 0 && !L.rel) || (s.att_vmix && !L.have_vmix && i != M->vmix_first))
+        return fail(-5, "layer %d: missing attention tensors (mix.sink, rel, vmix)", i);
+      if (s.att_rel_max > 0) {   // distance -> bucket, in double: below half the buckets one distance each, then logarithmic steps up to att_rel_max
+        const int B = L.rel_rows, half = B / 2, D = s.att_rel_max;
+        if (D <= half) return fail(-5, "layer %d: distance limit %d must exceed half of the %d distance buckets", i, D, B);
+        std::vector<int> bk((size_t)D + 1);
+        for (int n = 0; n <= D; n++)
+          bk[n] = n < half ? n : std::min(B - 1, half + (int)std::floor(std::log((double)n / half) / std::log((double)D / half) * (B - half)));
+        if (!L.rel_bucket && dmalloc(m, (void**)&L.rel_bucket, bk.size() * 4)) return -2;
+        CK(cudaMemcpy(L.rel_bucket, bk.data(), bk.size() * 4, cudaMemcpyHostToDevice));
+      }
+    } else if (s.mixer == DSK_MIX_MLA) {
+      L.in2.present = L.have_in2[0] && L.have_in2[1];
+      if (!L.in2.present || !L.dq_norm || !L.dkv_norm || !L.uq.present || !L.ukT.present || !L.uk.present || !L.uv.present || !L.o.present || (s.att_out_gate && !L.gmat.present))
+        return fail(-5, "layer %d: missing latent-attention tensors (mix.dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o)", i);
     } else if (is_ssd(s)) {
       if (!L.in.present || !L.o.present || !L.conv_w || !L.conv_b || !L.dt_bias || !L.A_log || !L.D || !L.mnorm)
         return fail(-5, "layer %d: missing state-space mixer tensors (mix.in, conv, conv.b, dt_bias, A_log, D, norm, o)", i);
@@ -447,7 +626,9 @@ static int finalize(dsk_model* m) {
       if (!L.q.present || !L.ukT.present || !L.uk.present || !L.uv.present || !L.o.present) return fail(-5, "layer %d: missing latent-attention tensors (mix.q, uk, uv, o)", i);
       if (s.att_kv_from < 0 && (!L.dkv.present || !L.dkv_norm)) return fail(-5, "layer %d: missing mix.dkv / mix.dkv.norm", i);
     }
-    if (s.ff_kind == DSK_FF_DENSE && (!L.up.present || !L.down.present || !L.up_b || !L.down_b || !L.act))
+    if (s.ff_kind == DSK_FF_DENSE && s.ff_act == DSK_ACT_GEGLU) {
+      if (!L.gate_d.present || !L.up.present || !L.down.present) return fail(-5, "layer %d: missing feed-forward tensors (mlp.gate, up, down)", i);
+    } else if (s.ff_kind == DSK_FF_DENSE && (!L.up.present || !L.down.present || !L.up_b || !L.down_b || !L.act))
       return fail(-5, "layer %d: missing feed-forward tensors (mlp.up, up.b, down, down.b, act)", i);
     if (s.ff_kind == DSK_FF_MOE) {
       if (!L.router || !L.correction) return fail(-5, "layer %d: missing mlp.router / mlp.correction", i);
@@ -465,24 +646,34 @@ static double active_bytes(const dsk_model* m) {
   const Model* M = m->hy;
   const dsk_hybrid_config& c = M->c;
   const double ws = (double)M->wsize, W = c.dim;
-  double tot = W * ws + (double)c.vocab_size * W * ws + W * 4;
+  double tot = W * ws * (c.bigram_buckets > 0 ? 2 : 1) + (double)c.vocab_size * W * ws + W * 4;
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
     double mat = 0, f32 = W;
     if (R.pass >= 0) f32 += W;
     if (c.block == DSK_BLOCK_SANDWICH) f32 += W * (s.ff_kind != DSK_FF_NONE ? 3 : 1);
+    if (c.block == DSK_BLOCK_POST) {   // per sublayer: convolution taps, gate matrix and bias (the closing weight is the W counted above)
+      const double subs = s.ff_kind != DSK_FF_NONE ? 2 : 1;
+      f32 += subs * (W * c.canon_taps + (c.res_gate ? W : 0)) + (subs - 1) * W;
+      if (c.res_gate) mat += subs * W * W;
+    }
     if (s.mixer == DSK_MIX_GQA) {
-      const double HD = (double)s.att_heads * s.att_dim, GD = (double)s.att_kv_heads * s.att_dim;
-      mat += (HD + GD) * W + W * s.att_heads * s.att_vdim;
-      f32 += HD + GD + (s.att_talk ? (double)s.att_heads * s.att_heads : 0.0);
+      const double HD = (double)s.att_heads * s.att_dim, GD = (double)s.att_kv_heads * s.att_dim, GV = s.att_value_proj ? (double)s.att_kv_heads * s.att_vdim : 0.0;
+      mat += (HD + GD + GV) * W + W * s.att_heads * s.att_vdim;
+      f32 += HD + GD + (s.att_talk ? (double)s.att_heads * s.att_heads : 0.0) + (s.att_bias ? HD + GD + GV : 0.0) + (s.att_sink ? s.att_heads : 0);
+    } else if (s.mixer == DSK_MIX_MLA) {
+      const double H = s.att_heads, DK = s.att_dim + s.att_rot_dim, Rr = s.att_kv_rank, Q = s.att_q_rank;
+      mat += (Q + Rr + s.att_rot_dim) * W + H * DK * Q + H * (s.att_dim + s.att_vdim) * Rr + (s.att_out_gate ? H * s.att_vdim * W : 0.0) + W * H * s.att_vdim;
+      f32 += Q + Rr;
     } else if (is_ssd(s)) { mat += (double)ssd_proj(s) * W + W * ssd_inner(s); f32 += (double)ssd_channels(s) * (s.ssm_conv + 1) + 3.0 * s.ssm_heads + ssd_inner(s); }
     else {
       mat += (double)s.att_heads * s.att_dim * W + (double)s.att_heads * (s.att_dim + s.att_vdim) * s.att_kv_rank + W * s.att_heads * s.att_vdim;
       if (s.att_kv_from < 0) { mat += (double)s.att_kv_rank * W; f32 += s.att_kv_rank; }
     }
     if (s.ff_kind == DSK_FF_MOE) { mat += 3.0 * s.ff_top * s.ff_hidden * W; f32 += (double)s.ff_experts * (W + 1); }
-    if (s.ff_kind == DSK_FF_DENSE) { mat += 2.0 * s.ff_hidden * W; f32 += s.ff_hidden + W; }
+    if (s.ff_kind == DSK_FF_DENSE && s.ff_act == DSK_ACT_GEGLU) mat += 3.0 * s.ff_hidden * W;
+    else if (s.ff_kind == DSK_FF_DENSE) { mat += 2.0 * s.ff_hidden * W; f32 += s.ff_hidden + W; }
     if (c.side_dim > 0) { mat += 2.0 * c.side_dim * W + c.side_dim; f32 += W; }
     tot += mat * ws + f32 * 4;
   }
@@ -494,14 +685,17 @@ static bool fused_norms(const dsk_hybrid_config& c);
 static int launches_per_token(const dsk_model* m) {
   const Model* M = m->hy;
   int n = fused_norms(M->c) ? 3 : 4;
-  const bool sandwich = M->c.block == DSK_BLOCK_SANDWICH;
+  if (M->c.bigram_buckets > 0) n += 1;
+  const bool sandwich = M->c.block == DSK_BLOCK_SANDWICH, post = M->c.block == DSK_BLOCK_POST;
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
+    if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.canon_taps > 0 ? 1 : 0) + (M->c.res_gate ? 1 : 0));   // convolution, gate, closing norm
+    else if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
     else n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
-    if (s.mixer == DSK_MIX_GQA) n += 6;   // q, k, norm + rotation, attention, merge, o
-    else n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
+    if (s.mixer == DSK_MIX_GQA) n += s.att_value_proj ? 5 : 6;   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, o
+    else if (s.mixer == DSK_MIX_MLA) n += 10 + (s.att_out_gate ? 1 : 0);   // down-projections, query norm, query up, latent preparation, absorbed query, attention, merge, value up, (gate,) o
+    else if (s.mixer != DSK_MIX_MLA) n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
     if (s.ff_kind == DSK_FF_MOE) n += 5;
     if (s.ff_kind == DSK_FF_DENSE) n += 2;
     if (M->c.side_dim > 0) n += 3;
@@ -526,6 +720,7 @@ static int state_reset(dsk_state* s) {
     if (l.hist) CK(cudaMemsetAsync(l.hist, 0, l.hist_bytes, s->stream));
     if (l.cache) CK(cudaMemsetAsync(l.cache, 0, l.cache_bytes, s->stream));
     if (l.vcache) CK(cudaMemsetAsync(l.vcache, 0, l.vcache_bytes, s->stream));
+    if (l.canon) CK(cudaMemsetAsync(l.canon, 0, l.canon_bytes, s->stream));
   }
   S->next_pos = 0;
   s->last_pos = -1;
@@ -558,19 +753,34 @@ static dsk_state* state_create(dsk_model* m) {
   size_t mx0 = c.dim, mx1 = c.dim, mx2 = c.dim, mx3 = c.dim, mxE = 1, mxTop = 1;
   S->L.resize(M->runs.size());   // one state per layer run
   bool any_talk = false;
+  size_t mxGV = 0;
   for (size_t r = 0; r < M->runs.size(); r++) {
     const int i = M->runs[r].layer;
     const HLayer& L = M->L[i];
     const dsk_layer_spec& sp = L.sp;
     LayerState& ls = S->L[r];
+    if (c.block == DSK_BLOCK_POST && c.canon_taps > 1) {
+      ls.canon_bytes = (size_t)2 * (c.canon_taps - 1) * c.dim * 4;
+      if (salloc(S, (void**)&ls.canon, ls.canon_bytes)) return nullptr;
+    }
     if (sp.mixer == DSK_MIX_GQA) {
       const size_t HD = (size_t)sp.att_heads * sp.att_dim, GD = (size_t)sp.att_kv_heads * sp.att_dim, GV = (size_t)sp.att_kv_heads * sp.att_vdim;
-      ls.cache_bytes = (size_t)L.ring * GD * 4;
-      ls.vcache_bytes = (size_t)L.ring * GV * 4;
+      const size_t rows = (size_t)sp.att_keep_first + L.ring;   // the kept first positions have rows of their own in front of the ring
+      ls.cache_bytes = rows * GD * 4;
+      ls.vcache_bytes = rows * GV * 4;
       if (salloc(S, &ls.cache, ls.cache_bytes) || salloc(S, &ls.vcache, ls.vcache_bytes)) return nullptr;
-      mx0 = std::max<size_t>(mx0, HD); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
+      mx0 = std::max<size_t>(mx0, sp.att_value_proj ? HD + GD + GV : HD); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
       mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_vdim);
       any_talk |= sp.att_talk != 0;
+      if (sp.att_vmix) mxGV = std::max(mxGV, GV);
+    } else if (sp.mixer == DSK_MIX_MLA) {
+      const size_t H = sp.att_heads, RW = (size_t)sp.att_kv_rank + sp.att_rot_dim;
+      ls.cache_bytes = (size_t)L.ring * RW * 4;
+      if (salloc(S, &ls.cache, ls.cache_bytes)) return nullptr;
+      mx0 = std::max<size_t>(mx0, std::max(H * (sp.att_dim + sp.att_rot_dim), H * sp.att_vdim));
+      mx1 = std::max<size_t>(mx1, sp.att_q_rank + RW);
+      mx2 = std::max<size_t>(mx2, std::max<size_t>(sp.att_q_rank, H * RW));
+      mx3 = std::max<size_t>(mx3, std::max(H * RW, H * sp.att_vdim));
     } else if (is_ssd(sp)) {
       ls.ssm_bytes = (size_t)sp.ssm_heads * sp.ssm_vdim * sp.ssm_state * 4;
       ls.hist_bytes = (size_t)std::max(1, sp.ssm_conv - 1) * ssd_channels(sp) * 4;
@@ -601,32 +811,39 @@ static dsk_state* state_create(dsk_model* m) {
   for (const HLayer& L : M->L) {
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_kv_rank + 2));
     if (L.sp.mixer == DSK_MIX_GQA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_vdim + 2));
+    if (L.sp.mixer == DSK_MIX_MLA) mxPart = std::max(mxPart, (size_t)kAttnSplitTokens * L.sp.att_heads * kAttnSplitMax * (L.sp.att_kv_rank + L.sp.att_rot_dim + 2));
   }
   rc |= salloc(S, (void**)&S->part, mxPart * 4);
   if ((int)Tc >= kPrefillMin) {   // buffers of the matrix-product attention path, unless a window is too long for them
     // latent attention up-projects keys and values of all heads (fp32, then packed in the matrix type); grouped-query
     // attention packs its cached key / value heads in fp32 (kf / vf) and needs a second score array when it mixes heads
-    size_t keys = 0, hd = 0, hv = 0, heads = 0;
+    // (latent attention with a rotated key part packs in fp32: its scores are 32-bit products)
+    size_t keys = 0, hd = 0, hv = 0, heads = 0, pack_es = 0;
     bool latent = false;
     for (const HLayer& L : M->L) {
       if (L.sp.mixer == DSK_MIX_SSD) continue;
       const size_t kh = L.sp.mixer == DSK_MIX_GQA ? L.sp.att_kv_heads : L.sp.att_heads;
-      latent |= L.sp.mixer == DSK_MIX_LATENT_SWA;
-      keys = std::max<size_t>(keys, (size_t)std::min<long long>((long long)L.sp.att_window - 1, (long long)c.max_seq_len) + std::min<size_t>(Tc, kPrefillQ));
-      hd = std::max<size_t>(hd, kh * L.sp.att_dim); hv = std::max<size_t>(hv, kh * L.sp.att_vdim);
+      latent |= L.sp.mixer == DSK_MIX_LATENT_SWA || L.sp.mixer == DSK_MIX_MLA;
+      if (L.sp.mixer == DSK_MIX_LATENT_SWA) pack_es = std::max(pack_es, M->wsize);
+      if (L.sp.mixer == DSK_MIX_MLA) pack_es = 4;
+      keys = std::max<size_t>(keys, (size_t)std::min<long long>((long long)L.sp.att_window - 1, (long long)c.max_seq_len) + std::min<size_t>(Tc, kPrefillQ) +
+                                        (L.sp.mixer == DSK_MIX_GQA ? L.sp.att_keep_first : 0));
+      hd = std::max<size_t>(hd, kh * (L.sp.att_dim + (L.sp.mixer == DSK_MIX_MLA ? L.sp.att_rot_dim : 0))); hv = std::max<size_t>(hv, kh * L.sp.att_vdim);
       heads = std::max<size_t>(heads, L.sp.att_heads);
     }
-    const size_t bytes = keys * (hd + hv) * (4 + (latent ? M->wsize : 0)) + heads * kPrefillQ * keys * 4 * (any_talk ? 2 : 1);
+    const size_t bytes = keys * (hd + hv) * (4 + (latent ? pack_es : 0)) + heads * kPrefillQ * keys * 4 * (any_talk ? 2 : 1);
     if (keys > 0 && bytes <= ((size_t)4 << 30)) {
       S->prefill_keys = (int)keys;
       rc |= salloc(S, (void**)&S->kf, keys * hd * 4) | salloc(S, (void**)&S->vf, keys * hv * 4);
-      if (latent) rc |= salloc(S, &S->kb, keys * hd * M->wsize) | salloc(S, &S->vt, keys * hv * M->wsize);
+      if (latent) rc |= salloc(S, &S->kb, keys * hd * pack_es) | salloc(S, &S->vt, keys * hv * pack_es);
       rc |= salloc(S, (void**)&S->sc, heads * kPrefillQ * keys * 4) | salloc(S, (void**)&S->d_rows, keys * 4);
       if (any_talk) rc |= salloc(S, (void**)&S->sc2, heads * kPrefillQ * keys * 4);
     }
   }
   rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
-  if (c.block == DSK_BLOCK_SANDWICH) rc |= salloc(S, (void**)&S->y, Tc * c.dim * 4);
+  if (c.block != DSK_BLOCK_PARALLEL) rc |= salloc(S, (void**)&S->y, Tc * c.dim * 4);
+  if (mxGV) rc |= salloc(S, (void**)&S->vfirst, Tc * mxGV * 4);
+  rc |= salloc(S, (void**)&S->d_prev, 16);
   rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
   rc |= salloc(S, (void**)&S->wgt, Tc * mxTop * 4) | salloc(S, (void**)&S->d_idx, Tc * mxTop * 4) | salloc(S, (void**)&S->d_perm, Tc * mxTop * 4);
   rc |= salloc(S, (void**)&S->d_tiles, (size_t)S->max_tiles * sizeof(int4)) | salloc(S, (void**)&S->d_ntiles, 16);
@@ -684,13 +901,15 @@ static GemmP gp(const float* A, int lda, const void* W, int ldw, float* C, int l
 }
 
 static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaStream_t st) {
-  const int bn = epi == HEPI_GLU ? 64 : 128;
+  const int bn = epi_dual(epi) ? 64 : 128;
   const dim3 grid((unsigned)((P.N + bn - 1) / bn), (unsigned)(P.tiles ? tile_cap : (P.M + 127) / 128), (unsigned)Z);
   switch (epi) {
     case HEPI_STORE: gemm_mma<HEPI_STORE><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_ADD: gemm_mma<HEPI_ADD><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_GLU: gemm_mma<HEPI_GLU><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_XIELU: gemm_mma<HEPI_XIELU><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_GEGLU: gemm_mma<HEPI_GEGLU><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_SIGMUL: gemm_mma<HEPI_SIGMUL><<<grid, 256, kMmaSmem, st>>>(P); break;
     default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, kMmaSmem, st>>>(P); break;
   }
 }
@@ -704,6 +923,8 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_ADD: gemv_rows<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GLU: gemv_rows<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_XIELU: gemv_rows<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_GEGLU: gemv_rows<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_SIGMUL: gemv_rows<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
       default: gemv_rows<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   } else {
@@ -713,6 +934,8 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_ADD: gemm_tiled<WT, HEPI_ADD><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GLU: gemm_tiled<WT, HEPI_GLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_XIELU: gemm_tiled<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_GEGLU: gemm_tiled<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_SIGMUL: gemm_tiled<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
       default: gemm_tiled<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   }
@@ -808,12 +1031,17 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   State* S = s->hy;
   const dsk_hybrid_config& c = M->c;
   const bool bf = c.quant == DSK_BF16;
-  const bool sandwich = c.block == DSK_BLOCK_SANDWICH;
+  const bool sandwich = c.block == DSK_BLOCK_SANDWICH, post = c.block == DSK_BLOCK_POST;
   const int W = c.dim;
   const float mult = c.residual_mult;
-  if (bf) embed_rows<__nv_bfloat16><<<T, 256, 0, st>>>(S->d_tok, (const __nv_bfloat16*)M->embed.p, W, S->x);
-  else embed_rows<float><<<T, 256, 0, st>>>(S->d_tok, (const float*)M->embed.p, W, S->x);
+  const float es = c.embed_scale != 0.f ? c.embed_scale : 1.f;
+  const int nb = c.bigram_buckets;
+  if (bf) embed_rows<__nv_bfloat16><<<T, 256, 0, st>>>(S->d_tok, (const __nv_bfloat16*)M->embed.p, W, S->x, es, nb > 0 ? (const __nv_bfloat16*)M->bigram.p : nullptr,
+                                                       nb, c.bigram_mul_prev, c.bigram_mul_cur, S->d_ctl, S->d_prev);
+  else embed_rows<float><<<T, 256, 0, st>>>(S->d_tok, (const float*)M->embed.p, W, S->x, es, nb > 0 ? (const float*)M->bigram.p : nullptr, nb, c.bigram_mul_prev,
+                                            c.bigram_mul_cur, S->d_ctl, S->d_prev);
   S->launches++;
+  if (nb > 0) { carry_token<<<1, 1, 0, st>>>(S->d_tok, T, S->d_prev); S->launches++; }   // the next step's first token pairs with this step's last
   if (pos0 < 0) S->tl_used = 0;   // a captured step records no events
   const bool tl = S->timeline && pos0 >= 0;
   auto MK = [&](const char* label) { if (tl) mark(S, label, st); };
@@ -828,7 +1056,28 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     const HLayer& L = M->L[li];
     const dsk_layer_spec& sp = L.sp;
     LayerState& ls = S->L[ri];
-    if (!h_ready) {
+    // post-norm blocks: a sublayer reads u = x + conv(x) (S->h; the stream itself without a convolution); afterwards its result y is gated
+    // by sigmoid(rg x + b), normalised with the folded weight (norm x layer scale) and added to the stream
+    auto open_post = [&](const float* taps, int which) -> const float* {
+      if (c.canon_taps <= 0) return S->x;
+      float* ring = ls.canon ? ls.canon + (size_t)which * (c.canon_taps - 1) * W : nullptr;
+      const int ty = (T + kCanonTokens - 1) / kCanonTokens;
+      canon_conv<<<dim3((unsigned)((W + 127) / 128), (unsigned)ty), 128, 0, st>>>(S->x, W, taps, ring, S->h, W, T, W, c.canon_taps, S->d_ctl);
+      S->launches++;
+      if (ty > 1 && c.canon_taps > 1) { canon_history<<<(W + 127) / 128, 128, 0, st>>>(S->x, W, ring, T, W, c.canon_taps, S->d_ctl); S->launches++; }
+      return S->h;
+    };
+    auto close_post = [&](const HTensor& rg, const float* rg_b, const float* close_w) {
+      if (c.res_gate) {
+        GemmP G = gp(S->x, W, rg.p, W, S->y, W, T, W, W);
+        G.bias = rg_b;
+        linear(S, bf, HEPI_SIGMUL, G, 1, st);
+      }
+      norm_rows(c, S, S->y, close_w, S->x, T, 1, mult, st);
+    };
+    const float* hin = S->h;   // what the mixer reads
+    if (post) hin = open_post(L.canon1, 0);
+    else if (!h_ready) {
       if (run.pass >= 0) {   // a pass of the layer loop opens with its own vector added to the residual stream
         add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
         S->launches++;
@@ -845,24 +1094,38 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       S->launches++;
       h_ready = true;
     };
-    const Sink sink = sandwich ? to_y : to_x;
+    const Sink sink = (sandwich || post) ? to_y : to_x;
     if (sp.mixer == DSK_MIX_GQA) {
       const int H = sp.att_heads, G = sp.att_kv_heads, D = sp.att_dim, V = sp.att_vdim, HD = H * D, GD = G * D, GV = G * V, rep = H / G;
+      const int keep = sp.att_keep_first;
       float *kc = (float*)ls.cache, *vc = (float*)ls.vcache;
+      const ScoreMods sm{sp.att_softcap, sp.att_rel_max > 0 ? L.rel : nullptr, L.rel_bucket, sp.att_rel_max, sp.att_sink ? L.sink : nullptr, keep};
       MK("norm");
-      linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
-      linear(S, bf, HEPI_STORE, gp(S->h, W, L.kproj.p, W, S->b1, GD, T, GD, W), 1, st);
-      MK("att.qk");
-      qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b1, nullptr, GD, GV, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims, L.rot_freq,
-                                      L.rot_mag, S->d_ctl, kc, vc, L.ring);
+      if (sp.att_value_proj) {   // one product for the stacked q / k / v rows; the first value-mixing layer keeps its values for the later ones
+        const int ld = HD + GD + GV;
+        GemmP P = gp(hin, W, L.qkv.p, W, S->b0, ld, T, ld, W);
+        P.bias = sp.att_bias ? L.qkv_b : nullptr;
+        linear(S, bf, HEPI_STORE, P, 1, st);
+        MK("att.qk");
+        const bool blend = sp.att_vmix && li != M->vmix_first;
+        qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b0 + HD, S->b0 + HD + GD, GD, GV, ld, ld, ld, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims,
+                                        L.rot_freq, L.rot_mag, S->d_ctl, kc, vc, L.ring, keep, blend ? S->vfirst : nullptr, L.vmix,
+                                        sp.att_vmix && li == M->vmix_first ? S->vfirst : nullptr);
+      } else {
+        linear(S, bf, HEPI_STORE, gp(hin, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
+        linear(S, bf, HEPI_STORE, gp(hin, W, L.kproj.p, W, S->b1, GD, T, GD, W), 1, st);
+        MK("att.qk");
+        qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b1, nullptr, GD, GV, HD, GD, GD, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims, L.rot_freq,
+                                        L.rot_mag, S->d_ctl, kc, vc, L.ring, keep, nullptr, 0.f, nullptr);
+      }
       S->launches++;
       MK("att.norm+rot");
       if (pos0 >= 0 && T >= kPrefillMin && S->prefill_keys > 0) {
         // a portion: blocks of kPrefillQ queries, each as  scores = q k^T per head (fp32);  mixing of the heads;  masked softmax;  o = P v
         for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
           const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
-          const int first = mask_first(sp.att_mask, sp.att_window, qpos0), Lk = qpos0 + Tq - first;
-          pack_ring_kv<float><<<Lk, 256, 0, st>>>(kc, vc, S->kf, S->vf, first, Lk, L.ring, G, D, V);
+          const int first = mask_first(sp.att_mask, sp.att_window, qpos0), nk = std::min(keep, first), Lk = nk + qpos0 + Tq - first;
+          pack_ring_kv<float><<<Lk, 256, 0, st>>>(kc, vc, S->kf, S->vf, first, Lk, L.ring, G, D, V, nk, keep);
           S->launches++;
           MK("att.pack");
           GemmP Sc = gp(S->b2 + (size_t)t0 * HD, HD, S->kf, D, S->sc, Lk, Tq, Lk, D);
@@ -876,7 +1139,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
             S->launches++;
             pr = S->sc2;
           }
-          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(pr, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window);
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(pr, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window, nk, sm);
           S->launches++;
           MK("att.softmax");
           GemmP Ov = gp(pr, Lk, S->vf, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
@@ -886,9 +1149,9 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         }
       } else {
         int NS = 1;
-        if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, L.ring) + 31) / 32, kAttnSplitMax));
+        if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, L.ring) + keep + 31) / 32, kAttnSplitMax));
         gqa_attn<<<dim3((unsigned)T, (unsigned)NS), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
-            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, NS, S->part);
+            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, NS, S->part, sm);
         if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(S->part, S->b3, V, NS);
         S->launches += NS > 1 ? 2 : 1;
         MK("att.decode");
@@ -897,10 +1160,74 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       P.alpha = sink.alpha;
       linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
+    } else if (sp.mixer == DSK_MIX_MLA) {
+      const int H = sp.att_heads, D = sp.att_dim, Rd = sp.att_rot_dim, DK = D + Rd, V = sp.att_vdim, R = sp.att_kv_rank, RW = R + Rd, Q = sp.att_q_rank;
+      float* cache = (float*)ls.cache;
+      const int ldi = Q + RW;
+      MK("norm");
+      linear(S, bf, HEPI_STORE, gp(hin, W, L.in2.p, W, S->b1, ldi, T, ldi, W), 1, st);              // [query latent | key / value latent | rotated key part]
+      group_rmsnorm<float><<<T, 256, 0, st>>>(S->b1, ldi, L.dq_norm, S->b2, Q, Q, 1, c.norm_eps, 0, 0.f, nullptr, 0);
+      S->launches++;
+      linear(S, bf, HEPI_STORE, gp(S->b2, Q, L.uq.p, Q, S->b0, H * DK, T, H * DK, Q), 1, st);       // q [T][H][D | Rd]
+      const bool portion = pos0 >= 0 && T >= kPrefillMin && S->prefill_keys > 0;
+      mla_prepare<<<T, 256, 0, st>>>(S->b1 + Q, ldi, L.dkv_norm, c.norm_eps, S->b0, portion ? nullptr : S->b2, H, D, Rd, R, sp.rot_dims, L.rot_freq,
+                                     S->d_ctl, cache, L.ring);
+      S->launches++;
+      MK("att.q+latent");
+      float* ov = S->b3;   // [T][H*V] heads' outputs
+      if (portion) {
+        // blocks of kPrefillQ queries: plain keys and values up-projected from the visible latents, the rotated key part appended to every
+        // head's keys; scores, softmax and the value product in fp32
+        for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
+          const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
+          const int first = mask_first(sp.att_mask, sp.att_window, qpos0), Lk = qpos0 + Tq - first;
+          ring_rows<<<(Lk + 255) / 256, 256, 0, st>>>(first, Lk, L.ring, S->d_rows);
+          GemmP K = gp(cache, RW, L.uk.p, R, S->kf, H * D, Lk, H * D, R);
+          K.a_map = S->d_rows;
+          linear(S, bf, HEPI_STORE, K, 1, st);
+          GemmP Vp = gp(cache, RW, L.uv.p, R, S->vf, H * V, Lk, H * V, R);
+          Vp.a_map = S->d_rows;
+          linear(S, bf, HEPI_STORE, Vp, 1, st);
+          MK("att.kv_up");
+          pack_mla_kv<<<Lk, 256, 0, st>>>(S->kf, S->vf, cache, S->d_rows, (float*)S->kb, (float*)S->vt, Lk, H, D, Rd, R, V);
+          MK("att.pack");
+          GemmP Sc = gp(S->b0 + (size_t)t0 * H * DK, H * DK, S->kb, DK, S->sc, Lk, Tq, Lk, DK);
+          Sc.sA = DK; Sc.sW = (long long)Lk * DK; Sc.sC = (long long)Tq * Lk; Sc.alpha = sp.att_scale;
+          linear(S, false, HEPI_STORE, Sc, H, st);
+          MK("att.scores");
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window, 0, ScoreMods{});
+          MK("att.softmax");
+          GemmP Ov = gp(S->sc, Lk, S->vt, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
+          Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.sC = V;
+          linear(S, false, HEPI_STORE, Ov, H, st);
+          MK("att.pv");
+          S->launches += 3;
+        }
+      } else {
+        {   // absorbed query: qa[t][h][0:R] = W_uk[h]^T q_plain[t][h]  (mla_prepare put the rotated part behind it)
+          GemmP P = gp(S->b0, H * DK, L.ukT.p, D, S->b2, H * RW, T, R, D);
+          P.sA = DK; P.sW = (long long)R * D; P.sC = RW;
+          linear(S, bf, HEPI_STORE, P, H, st);
+        }
+        launch_attn(S->b2, cache, S->b3, T, H, RW, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, S->part, st);
+        S->launches++;
+        {  // value up-projection per head from the first R entries of the weighted cache rows
+          GemmP P = gp(S->b3, H * RW, L.uv.p, R, S->b0, H * V, T, V, R);
+          P.sA = RW; P.sW = (long long)V * R; P.sC = V;
+          linear(S, bf, HEPI_STORE, P, H, st);
+        }
+        ov = S->b0;
+        MK("att.absorbed");
+      }
+      if (sp.att_out_gate) linear(S, bf, HEPI_SIGMUL, gp(hin, W, L.gmat.p, W, ov, H * V, T, H * V, W), 1, st);   // heads *= sigmoid(g u)
+      GemmP P = gp(ov, H * V, L.o.p, H * V, sink.C, W, T, W, H * V);
+      P.alpha = sink.alpha;
+      linear(S, bf, sink.epi, P, 1, st);
+      MK("att.o");
     } else if (is_ssd(sp)) {
       const int inner = (int)ssd_inner(sp), ch = (int)ssd_channels(sp), pw = (int)ssd_proj(sp);
       MK("norm");
-      linear(S, bf, HEPI_STORE, gp(S->h, W, L.in.p, W, S->b0, pw, T, pw, W), 1, st);
+      linear(S, bf, HEPI_STORE, gp(hin, W, L.in.p, W, S->b0, pw, T, pw, W), 1, st);
       MK("ssd.in");
       causal_conv_silu<<<dim3((unsigned)((ch + 127) / 128), (unsigned)T), 128, 0, st>>>(S->b0 + inner, pw, L.conv_w, L.conv_b, ls.hist, S->b1, ch, T, ch, sp.ssm_conv);
       if (sp.ssm_conv > 1) conv_history_update<<<(ch + 127) / 128, 128, 0, st>>>(S->b0 + inner, pw, ls.hist, T, ch, sp.ssm_conv);
@@ -919,9 +1246,9 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       const HLayer& O = M->L[L.owner];
       float* cache = (float*)S->L[R0(M, ri)].cache;
       MK("norm");
-      linear(S, bf, HEPI_STORE, gp(S->h, W, L.q.p, W, S->b0, H * D, T, H * D, W), 1, st);
+      linear(S, bf, HEPI_STORE, gp(hin, W, L.q.p, W, S->b0, H * D, T, H * D, W), 1, st);
       if (L.owner == li) {
-        linear(S, bf, HEPI_STORE, gp(S->h, W, L.dkv.p, W, S->b1, R, T, R, W), 1, st);
+        linear(S, bf, HEPI_STORE, gp(hin, W, L.dkv.p, W, S->b1, R, T, R, W), 1, st);
         group_rmsnorm<float><<<T, 256, 0, st>>>(S->b1, R, L.dkv_norm, cache, R, R, 1, c.norm_eps, 0, 0.f, S->d_ctl, O.ring);
         S->launches++;
       }
@@ -948,7 +1275,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           MK("att.pack");
           linear(S, bf, HEPI_STORE, Sc, H, st);
           MK("att.scores");
-          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window);
+          softmax_band<<<dim3((unsigned)Tq, (unsigned)H), 128, 0, st>>>(S->sc, Tq, Lk, first, qpos0, sp.att_mask, sp.att_window, 0, ScoreMods{});
           GemmP Ov = gp(S->sc, Lk, S->vt, Lk, S->b3 + (size_t)t0 * H * V, H * V, Tq, V, Lk);
           Ov.sA = (long long)Tq * Lk; Ov.sW = (long long)V * Lk; Ov.sC = V;
           MK("att.softmax");
@@ -976,6 +1303,11 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
     }
+    if (post) {   // the mixer's result closes; the feed-forward opens on the new stream
+      close_post(L.rg1, L.rg1_b, L.close1);
+      if (sp.ff_kind != DSK_FF_NONE) hin = open_post(L.canon2, 1);
+      MK("norm");
+    }
     if (sandwich) {   // x += norm1b(mixer output); the feed-forward then reads norm2 of the new x
       if (sp.ff_kind == DSK_FF_NONE) close_run(L.norm1b);
       else if (fuse) {
@@ -987,9 +1319,19 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       }
       MK("norm");
     }
-    if (sp.ff_kind == DSK_FF_DENSE) {
+    if (sp.ff_kind == DSK_FF_DENSE && sp.ff_act == DSK_ACT_GEGLU) {
       const int ff = sp.ff_hidden;
-      GemmP U = gp(S->h, W, L.up.p, W, S->b2, ff, T, ff, W);
+      GemmP U = gp(hin, W, L.gate_d.p, W, S->b2, ff, T, ff, W);
+      U.W2 = L.up.p;
+      linear(S, bf, HEPI_GEGLU, U, 1, st);
+      MK("ff.up");
+      GemmP Dn = gp(S->b2, ff, L.down.p, ff, sink.C, W, T, W, ff);
+      Dn.alpha = sink.alpha;
+      linear(S, bf, sink.epi, Dn, 1, st);
+      MK("ff.down");
+    } else if (sp.ff_kind == DSK_FF_DENSE) {
+      const int ff = sp.ff_hidden;
+      GemmP U = gp(hin, W, L.up.p, W, S->b2, ff, T, ff, W);
       U.bias = L.up_b; U.act_a = L.act_a; U.act_b = L.act_b;
       linear(S, bf, HEPI_XIELU, U, 1, st);
       MK("ff.up");
@@ -1000,11 +1342,11 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     if (sp.ff_kind == DSK_FF_MOE) {
       const int E = sp.ff_experts, top = sp.ff_top, ff = sp.ff_hidden, pairs = T * top;
-      linear(S, false, HEPI_STORE, gp(S->h, W, L.router, W, S->b0, E, T, E, W), 1, st);   // router: fp32 weights in every mode
+      linear(S, false, HEPI_STORE, gp(hin, W, L.router, W, S->b0, E, T, E, W), 1, st);   // router: fp32 weights in every mode
       moe_route<<<T, 128, (size_t)(2 * E + top) * 4, st>>>(S->b0, L.correction, E, top, sp.ff_router_scale, S->d_idx, S->wgt);
       S->launches++;
       MK("moe.router");
-      GemmP G = gp(S->h, W, L.gate_s.p, W, S->b2, ff, pairs, ff, W);
+      GemmP G = gp(hin, W, L.gate_s.p, W, S->b2, ff, pairs, ff, W);
       G.W2 = L.up_s.p; G.sW = (long long)ff * W; G.lim = sp.ff_limit;
       GemmP Dn = gp(S->b2, ff, L.down_s.p, ff, S->b3, W, pairs, W, ff);
       Dn.sW = (long long)ff * W;
@@ -1033,6 +1375,10 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     if (sandwich && sp.ff_kind != DSK_FF_NONE) {
       close_run(L.norm2b);
+      MK("norm");
+    }
+    if (post && sp.ff_kind != DSK_FF_NONE) {
+      close_post(L.rg2, L.rg2_b, L.close2);
       MK("norm");
     }
     if (c.side_dim > 0) {

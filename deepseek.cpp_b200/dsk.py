@@ -23,11 +23,11 @@ sys.path.insert(0, HERE)
 import dseek  # noqa: E402
 
 QUANT_IDS = {"fp32": 0, "fp16": 1, "f8e5m2": 2, "q2_k": 3, "q3_k": 4, "bf16": 5}
-MIX_SSD, MIX_LATENT_SWA, MIX_GQA = 0, 1, 2
+MIX_SSD, MIX_LATENT_SWA, MIX_GQA, MIX_MLA = 0, 1, 2, 3
 FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
 MASK_WINDOW, MASK_CHUNK = 0, 1
-ACT_XIELU = 0
-BLOCK_PARALLEL, BLOCK_SANDWICH = 0, 1
+ACT_XIELU, ACT_GEGLU = 0, 1
+BLOCK_PARALLEL, BLOCK_SANDWICH, BLOCK_POST = 0, 1, 2
 NORM_RMS, NORM_LAYER = 0, 1
 HYDRATE_KV_CACHE, OUTPUT_LOGITS = 0, 1
 
@@ -94,7 +94,9 @@ class LayerSpec(C.Structure):
                [("att_scale", C.c_float)] + [(n, C.c_int) for n in ("ff_kind", "ff_experts", "ff_top", "ff_hidden")] + \
                [("ff_limit", C.c_float), ("ff_router_scale", C.c_float)] + \
                [(n, C.c_int) for n in ("att_mask", "att_kv_heads", "att_talk", "rot_dims", "rot_original")] + \
-               [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_fast", "rot_slow")] + [("ff_act", C.c_int)]
+               [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_fast", "rot_slow")] + [("ff_act", C.c_int)] + \
+               [(n, C.c_int) for n in ("att_value_proj", "att_bias", "att_keep_first", "att_rel_max", "att_sink", "att_vmix")] + \
+               [("att_softcap", C.c_float)] + [(n, C.c_int) for n in ("att_q_rank", "att_rot_dim", "att_out_gate")]
 
 
 class HybridConfig(C.Structure):
@@ -102,7 +104,9 @@ class HybridConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dim", "vocab_size", "n_layers", "max_seq_len", "quant", "chunk")] + \
                [("norm_eps", C.c_float), ("norm_groups", C.c_int), ("residual_mult", C.c_float), ("logit_scale", C.c_float),
                 ("side_dim", C.c_int)] + \
-               [(n, C.c_int) for n in ("block", "norm_kind", "tie_head", "loop_start", "loop_stop", "loop_times")]
+               [(n, C.c_int) for n in ("block", "norm_kind", "tie_head", "loop_start", "loop_stop", "loop_times")] + \
+               [("embed_scale", C.c_float)] + \
+               [(n, C.c_int) for n in ("bigram_buckets", "bigram_mul_prev", "bigram_mul_cur", "norm_scalar", "canon_taps", "res_gate", "layer_scale")]
 
 
 # mixer "type" strings of a layer-list config.json -> mixer kernel family.  Two names may map to one mechanism.
@@ -206,11 +210,67 @@ def rutulix_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, ch
     return hc, specs
 
 
+def sakusun_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chunk: int = 256):
+    """config.json of the Sakusun design -> (HybridConfig, LayerSpec array): post-norm blocks (input convolution, gated sublayer
+    results, single-number RMS norms, layer scale), a scaled token embedding plus a bigram table, and per layer either grouped-query
+    attention (value matrix, biases, whole-projection query / key norm, score cap, distance-bucket bias, window with kept first
+    positions, sink, value mixing) or latent attention with a query latent, a shared rotated key part and an output gate; gated
+    GELU feed-forwards; an untied head.  Keys a mixer does not have switch that part off."""
+    hc = HybridConfig()
+    layers = cfg["layers"]
+    hc.dim, hc.vocab_size, hc.n_layers = int(cfg["width"]), int(cfg["vocab"]), len(layers)
+    hc.quant, hc.chunk = QUANT_IDS[quant], int(chunk)
+    hc.max_seq_len = int(max_seq_len) if max_seq_len else 1 << 30
+    hc.norm_eps, hc.norm_groups = float(cfg["norm"]["eps"]), 1
+    hc.residual_mult, hc.logit_scale, hc.side_dim = 1.0, 1.0, 0
+    hc.block, hc.norm_kind, hc.tie_head, hc.norm_scalar = BLOCK_POST, NORM_RMS, 0, 1
+    hc.loop_start = hc.loop_stop = hc.loop_times = 0
+    emb = cfg.get("embedding") or {}
+    hc.embed_scale = float(emb.get("scale", 1.0))
+    bg = emb.get("bigram")
+    if bg:
+        hc.bigram_buckets, hc.bigram_mul_prev, hc.bigram_mul_cur = int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])
+    hc.canon_taps = int((cfg.get("canon") or {}).get("taps", 0))
+    hc.res_gate, hc.layer_scale = 1, 1
+    specs = (LayerSpec * len(layers))()
+    for i, lc in enumerate(layers):
+        sp, mx = specs[i], lc["mixer"]
+        sp.att_kv_from = -1
+        mask = mx.get("mask") or {}
+        sp.att_mask = MASK_WINDOW
+        sp.att_window = int(mask["size"]) if "size" in mask else 1 << 30      # no window: every earlier token is visible
+        sp.att_heads, sp.att_dim, sp.att_vdim, sp.att_scale = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"]), float(mx["scale"])
+        if lc["type"] == "attention":
+            sp.mixer = MIX_GQA
+            sp.att_kv_heads = int(mx.get("kv_heads", mx["heads"]))
+            sp.att_value_proj, sp.att_bias, sp.att_sink, sp.att_talk = 1, 1, 1, 0
+            sp.att_keep_first = int(mask.get("keep_first", 0)) if "size" in mask else 0
+            sp.att_softcap = float(mx.get("softcap") or 0.0)
+            sp.att_rel_max = int(mx.get("bias_max") or 0)
+            sp.att_vmix = 1 if mx.get("v_mix") else 0
+            sp.rot_dims, sp.rot_factor = 0, 0.0
+        elif lc["type"] == "latent_attention":
+            sp.mixer = MIX_MLA
+            sp.att_kv_rank, sp.att_q_rank, sp.att_rot_dim, sp.att_out_gate = int(mx["kv_rank"]), int(mx["q_rank"]), int(mx["rot_dim"]), 1
+            rot = mx.get("rot") or {}
+            sp.rot_dims, sp.rot_base, sp.rot_factor = int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), 0.0
+        else:
+            raise DskError(f"layer {i}: unknown mixer type {lc['type']!r}")
+        ff = lc.get("mlp")
+        if ff:
+            if ff.get("kind") != "dense":
+                raise DskError(f"layer {i}: unknown feed-forward kind {ff.get('kind')!r}")
+            sp.ff_kind, sp.ff_hidden, sp.ff_act = FF_DENSE, int(ff["ff"]), ACT_GEGLU
+        else:
+            sp.ff_kind = FF_NONE
+    return hc, specs
+
+
 # config.json "architecture" -> builder of the C-ABI model description (the DeepSeek families come as .dseek metadata instead)
-ARCHITECTURES = {"Desarax": hybrid_from_config, "Rutulix": rutulix_from_config}
+ARCHITECTURES = {"Desarax": hybrid_from_config, "Rutulix": rutulix_from_config, "Sakusun": sakusun_from_config}
 
 _lib = None
-ABI_VERSION = 5   # DSK_ABI_VERSION (include/dsk.h)
+ABI_VERSION = 6   # DSK_ABI_VERSION (include/dsk.h)
 
 
 def build(force: bool = False) -> str:

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DSK_ABI_VERSION 5
+#define DSK_ABI_VERSION 6
 
 /* Quant: src/codec.h:79-85 (same numbering) */
 enum { DSK_F32 = 0, DSK_F16 = 1, DSK_F8E5M2 = 2, DSK_Q2_K = 3, DSK_Q3_K = 4,
@@ -67,16 +67,33 @@ typedef struct dsk_config {
  * a per-layer token embedding gated by gelu_tanh(side.gate x) is projected, RMS-normed and added (x += residual_mult * ...).
  * (That is DSK_BLOCK_PARALLEL with DSK_NORM_RMS, the Desarax design; the Rutulix design is DSK_BLOCK_SANDWICH with
  * DSK_NORM_LAYER, DSK_MIX_GQA mixers, DSK_FF_DENSE feed-forwards, an untied head and a layer loop.) */
-enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2 };
+enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2, DSK_MIX_MLA = 3 };
 enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1, DSK_FF_DENSE = 2 };
 enum { DSK_MASK_WINDOW = 0,   /* position i sees j with 0 <= i - j < att_window */
        DSK_MASK_CHUNK = 1 };  /* position i sees j <= i with floor(i / att_window) == floor(j / att_window): borders at multiples of att_window in sequence positions */
-enum { DSK_ACT_XIELU = 0 };   /* z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2;  (p, q) = tensor mlp.act */
+enum { DSK_ACT_XIELU = 0,      /* z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2;  (p, q) = tensor mlp.act */
+       DSK_ACT_GEGLU = 1 };    /* gated: down(gelu_tanh(gate h) * (up h)), tensors mlp.gate / mlp.up / mlp.down, no biases */
 enum { DSK_BLOCK_PARALLEL = 0,   /* h = norm1(x); x += residual_mult (mixer(h) + ff(h)) */
-       DSK_BLOCK_SANDWICH = 1 }; /* x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))) */
+       DSK_BLOCK_SANDWICH = 1,   /* x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))) */
+       DSK_BLOCK_POST = 2 };     /* the sublayers read the stream itself and only their result is normalised:
+                                    u = x + conv(x) (canon_taps > 0; else u = x);  y = f(u) (* sigmoid(rg x + rg.b) with res_gate);
+                                    x += norm(y) (* ls with layer_scale), for f = mixer (tensors norm1, canon1, rg1, ls1), then feed-forward (..2) */
 enum { DSK_NORM_RMS = 0,         /* x / sqrt(mean(x^2) + eps) * w in norm_groups parts */
        DSK_NORM_LAYER = 1 };     /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, no bias */
-/*   DSK_MIX_GQA         softmax attention with att_heads query heads over att_kv_heads cached key heads (query head h reads key head
+/* DSK_MIX_GQA also has these switches (all off in the Rutulix design): att_value_proj (values = v matrix mix.v of att_vdim per
+ * key head instead of the raw key projection), att_bias (biases mix.q.b / k.b / v.b added in the projections), att_softcap > 0
+ * (score <- cap tanh(score / cap) after the scale), att_rel_max > 0 (a learned bias per distance bucket and head added after
+ * the cap: tensor mix.rel [B][heads], bucket(n) = n below B/2, else min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(att_rel_max / (B/2))
+ * (B - B/2)))), att_keep_first (DSK_MASK_WINDOW only: the first positions of a sequence stay visible beyond the window, at their
+ * true distance), att_sink (tensor mix.sink [heads]: e^sink joins the softmax denominator, with no key and no value), att_vmix (the
+ * first such layer's values v1 of a token are kept for the step; every later such layer caches (1 - l) v + l v1, l = tensor mix.vmix).
+ *   DSK_MIX_MLA         softmax attention over cached latents with a query latent and a rotated key part: c_q = rms(dq h) dq.norm,
+ *                       q = uq c_q laid out per head as [att_dim plain | att_rot_dim rotated]; dkv h = [att_kv_rank latent, RMS-normed
+ *                       with dkv.norm | att_rot_dim rotated key part shared by all heads]; per head key = uk c, value = uv c; score =
+ *                       att_scale (q_plain . k + q_rot . k_rot); rotation of the pairs (2i, 2i + 1) of the first rot_dims entries of the
+ *                       rotated part by pos * rot_base^(-2i / rot_dims); mask att_mask of size att_window; with att_out_gate the
+ *                       concatenated heads are multiplied by sigmoid(g h) before the output projection.  Caches [latent | rotated key].
+ *   DSK_MIX_GQA         softmax attention with att_heads query heads over att_kv_heads cached key heads (query head h reads key head
  *                       h / (att_heads / att_kv_heads)); a position's value vector is the raw output of its key matrix, taken ahead of the key norm and the rotation (no value matrix:
  *                       att_vdim == att_dim); RMS norm with a weight over the whole query projection and over the whole key
  *                       projection; rotary positions on the first rot_dims dimensions of every head, entries (2i, 2i + 1) of a head turning together,
@@ -97,6 +114,9 @@ typedef struct dsk_layer_spec {
   int rot_dims, rot_original;                                           /* rot_dims 0: no rotation */
   float rot_base, rot_factor, rot_fast, rot_slow;                       /* rot_factor <= 0: plain frequencies */
   int ff_act;                                                           /* DSK_FF_DENSE: DSK_ACT_*, hidden size ff_hidden */
+  int att_value_proj, att_bias, att_keep_first, att_rel_max, att_sink, att_vmix;   /* DSK_MIX_GQA switches (above) */
+  float att_softcap;
+  int att_q_rank, att_rot_dim, att_out_gate;                            /* DSK_MIX_MLA (with att_heads, att_dim, att_vdim, att_kv_rank, att_scale, att_mask, att_window, rot_dims, rot_base) */
 } dsk_layer_spec;
 typedef struct dsk_hybrid_config {
   int dim, vocab_size, n_layers;
@@ -113,6 +133,12 @@ typedef struct dsk_hybrid_config {
   int loop_start, loop_stop, loop_times;   /* layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights and a
                                               separate cache / state for every repetition; tensor loop.step [times][dim]: row t is added to the
                                               residual stream right before pass t (a loop of one pass still adds row 0).  loop_times 0: no loop */
+  float embed_scale;         /* token embedding rows are multiplied by this (0 reads as 1) */
+  int bigram_buckets, bigram_mul_prev, bigram_mul_cur;   /* > 0 buckets: row (prev * mul_prev + token * mul_cur) mod buckets of tensor "bigram"
+                                              [buckets + 1][dim] is added to the embedding; a sequence's first token takes the last row */
+  int norm_scalar;           /* 1: the weights of the norms outside the mixers (norm1, norm2, final.norm) are single numbers */
+  int canon_taps, res_gate, layer_scale;   /* DSK_BLOCK_POST: taps of the causal per-channel input convolution (tensors canon1 / canon2 [dim][taps], last tap on
+                                              the current token; 0: none), gated sublayer results (rg1 / rg2 [dim][dim] + .b), per-channel scale after the norm (ls1 / ls2) */
 } dsk_hybrid_config;
 
 typedef struct dsk_model dsk_model;
