@@ -218,9 +218,63 @@ static bool rutulix_config_from(const JValue& j, const std::string& quant, int c
   return true;
 }
 
+// The Sakusun design: post-norm blocks (input convolution, gated sublayer results, single-number RMS norms, layer scale), a scaled
+// token embedding plus a bigram table, grouped-query attention with its switches on (value matrix, biases, score cap, distance-bucket
+// bias, window with kept first positions, sink, value mixing) or latent attention with a query latent, a shared rotated key part and
+// an output gate, gated GELU feed-forwards, an untied head.
+static bool sakusun_config_from(const JValue& j, const std::string& quant, int context, dsk_hybrid_config* hc, std::vector<dsk_layer_spec>* specs) {
+  const JValue& layers = j.at("layers");
+  if (layers.kind != JValue::Arr || layers.arr.empty()) { fprintf(stderr, "FATAL: config.json has no layers\n"); return false; }
+  *hc = dsk_hybrid_config{};
+  hc->dim = j.integer("width", 0); hc->vocab_size = j.integer("vocab", 0); hc->n_layers = (int)layers.arr.size();
+  hc->max_seq_len = context > 0 ? context : 1 << 30;
+  hc->quant = quant == "fp32" ? DSK_F32 : DSK_BF16;
+  hc->chunk = context > 0 ? std::min(256, context) : 256;
+  hc->norm_eps = (float)j.at("norm").number("eps", 1e-5); hc->norm_groups = 1;
+  hc->residual_mult = 1.f; hc->logit_scale = 1.f;
+  hc->block = DSK_BLOCK_POST; hc->norm_kind = DSK_NORM_RMS; hc->tie_head = 0; hc->norm_scalar = 1;
+  const JValue& emb = j.at("embedding");
+  hc->embed_scale = (float)emb.number("scale", 1.0);
+  if (emb.has("bigram")) {
+    const JValue& bg = emb.at("bigram");
+    hc->bigram_buckets = bg.integer("buckets", 0); hc->bigram_mul_prev = bg.integer("mul_prev", 0); hc->bigram_mul_cur = bg.integer("mul_cur", 0);
+  }
+  hc->canon_taps = j.at("canon").integer("taps", 0);
+  hc->res_gate = 1; hc->layer_scale = 1;
+  for (size_t i = 0; i < layers.arr.size(); i++) {
+    const JValue& lc = layers.arr[i];
+    const JValue& mx = lc.at("mixer");
+    const JValue& mask = mx.at("mask");
+    const std::string type = lc.at("type").str;
+    dsk_layer_spec sp{};
+    sp.att_kv_from = -1; sp.att_mask = DSK_MASK_WINDOW; sp.att_window = mask.integer("size", 1 << 30);
+    sp.att_heads = mx.integer("heads", 0); sp.att_dim = mx.integer("dim", 0); sp.att_vdim = mx.integer("vdim", 0); sp.att_scale = (float)mx.number("scale", 1.0);
+    if (type == "attention") {
+      sp.mixer = DSK_MIX_GQA;
+      sp.att_kv_heads = mx.integer("kv_heads", sp.att_heads);
+      sp.att_value_proj = 1; sp.att_bias = 1; sp.att_sink = 1;
+      sp.att_keep_first = mask.has("size") ? mask.integer("keep_first", 0) : 0;
+      sp.att_softcap = (float)mx.number("softcap", 0.0); sp.att_rel_max = mx.integer("bias_max", 0);
+      sp.att_vmix = mx.has("v_mix") && mx.at("v_mix").kind == JValue::Bool && mx.at("v_mix").b;
+    } else if (type == "latent_attention") {
+      sp.mixer = DSK_MIX_MLA;
+      sp.att_kv_rank = mx.integer("kv_rank", 0); sp.att_q_rank = mx.integer("q_rank", 0); sp.att_rot_dim = mx.integer("rot_dim", 0); sp.att_out_gate = 1;
+      sp.rot_dims = mx.at("rot").integer("dims", 0); sp.rot_base = (float)mx.at("rot").number("base", 10000.0);
+    } else { fprintf(stderr, "FATAL: layer %zu: unknown mixer type %s\n", i, type.c_str()); return false; }
+    if (lc.has("mlp")) {
+      const JValue& ff = lc.at("mlp");
+      if (ff.at("kind").str != "dense") { fprintf(stderr, "FATAL: layer %zu: unknown feed-forward kind %s\n", i, ff.at("kind").str.c_str()); return false; }
+      sp.ff_kind = DSK_FF_DENSE; sp.ff_hidden = ff.integer("ff", 0); sp.ff_act = DSK_ACT_GEGLU;
+    }
+    specs->push_back(sp);
+  }
+  return true;
+}
+
 // config.json "architecture" -> builder of the C-ABI model description
 typedef bool (*ArchBuilder)(const JValue&, const std::string&, int, dsk_hybrid_config*, std::vector<dsk_layer_spec>*);
-static const struct { const char* name; ArchBuilder build; } kArchitectures[] = {{"Desarax", hybrid_config_from}, {"Rutulix", rutulix_config_from}};
+static const struct { const char* name; ArchBuilder build; } kArchitectures[] = {{"Desarax", hybrid_config_from}, {"Rutulix", rutulix_config_from},
+                                                                                {"Sakusun", sakusun_config_from}};
 
 // completion over token ids: the prompt goes through dsk_forward_chunk (prefill in portions), then the usual
 // dsk_sample -> dsk_forward loop; the ids are printed (these checkpoints carry no tokenizer).
@@ -234,7 +288,7 @@ static int run_layer_list(const std::string& dir, const std::string& quant, cons
   const std::string arch = cfg.at("architecture").str;
   ArchBuilder builder = nullptr;
   for (const auto& a : kArchitectures) if (arch == a.name) builder = a.build;
-  if (!builder) { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax, Rutulix)\n", arch.c_str()); return 1; }
+  if (!builder) { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax, Rutulix, Sakusun)\n", arch.c_str()); return 1; }
   if (quant != "bf16" && quant != "fp32") { fprintf(stderr, "FATAL: -q must be bf16 or fp32\n"); return 1; }
   std::vector<int> enc;
   for (size_t i = 0; i < prompt_ids.size();) {

@@ -1,7 +1,8 @@
 """hybrid_bench.py — prefill and decode throughput of the layer-list family at sizes that resemble a real model's layers.
 The Desarax sizes run beside the closest DeepSeek model of the framework (true-MLA blocks, fp16) at equal width / depth /
 experts; the Rutulix sizes run beside the closest layer-list model, a Desarax model of latent-attention layers at equal width,
-layer runs, heads, mask size and feed-forward matrix elements.
+layer runs, heads, mask size and feed-forward matrix elements; the Sakusun sizes run beside a Rutulix model (the framework's other
+attention-only design with dense feed-forwards) at equal width, depth, heads, window and feed-forward matrix elements.
 
 Used by `bench.py --hybrid`.  Random weights generated on the GPU (bf16), uploaded through dsk_upload_tensor(src_on_device).
 Decode is the device-side greedy loop (CUDA events around the captured step graph); prefill is dsk_forward_chunk over a prompt
@@ -26,7 +27,117 @@ SIZES = {
                           window=512, ff=4096, kv_rank=256),
     "rutulix_large": dict(design="Rutulix", width=2048, vocab=102400, n_layers=12, loop=(4, 8, 2), att_heads=16, kv_heads=4, att_dim=128, rot=64,
                           window=1024, ff=8192, kv_rank=512),
+    # Sakusun: pattern of latent-attention (L) and grouped-query attention (A) layers, gated feed-forwards of three matrices
+    "sakusun_small": dict(design="Sakusun", width=1024, vocab=32000, pattern="LALLLALA", att_heads=16, kv_heads=4, att_dim=64, window=512, keep=4,
+                          rel_rows=32, rel_max=1024, lat_dim=64, rot=32, kv_rank=256, q_rank=384, ff=2752, taps=4, buckets=65521),
+    "sakusun_large": dict(design="Sakusun", width=2048, vocab=102400, pattern="LALLLALLLALA", att_heads=16, kv_heads=4, att_dim=128, window=1024, keep=4,
+                          rel_rows=32, rel_max=2048, lat_dim=128, rot=64, kv_rank=512, q_rank=768, ff=5504, taps=4, buckets=65521),
 }
+
+
+def sakusun_config(z):
+    att = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5, "softcap": 50.0,
+           "bias_max": z["rel_max"], "mask": {"size": z["window"], "keep_first": z["keep"]}, "v_mix": True}
+    lat = {"heads": z["att_heads"], "dim": z["lat_dim"], "rot_dim": z["rot"], "vdim": z["lat_dim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "scale": (z["lat_dim"] + z["rot"]) ** -0.5, "rot": {"dims": z["rot"], "base": 10000.0}}
+    layers = [{"type": "attention" if ch == "A" else "latent_attention", "mixer": dict(att if ch == "A" else lat), "mlp": {"kind": "dense", "ff": z["ff"]}}
+              for ch in z["pattern"]]
+    return {"architecture": "Sakusun", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]},
+            "embedding": {"scale": 0.5, "bigram": {"buckets": z["buckets"], "mul_prev": 31, "mul_cur": 7}}}
+
+
+def closest_rutulix(z):
+    """The closest model of the framework to a Sakusun size: Rutulix layers (grouped-query attention, dense feed-forward of two
+    matrices with as many elements as the gated three), as many as the Sakusun model has, same width, heads and mask size."""
+    return dict(design="Rutulix", width=z["width"], vocab=z["vocab"], n_layers=len(z["pattern"]), loop=(0, 1, 1), att_heads=z["att_heads"],
+                kv_heads=z["kv_heads"], att_dim=z["att_dim"], rot=z["att_dim"] // 2, window=z["window"], ff=z["ff"] * 3 // 2, kv_rank=z["kv_rank"])
+
+
+def mint_sakusun(dsk, torch, cfg, z, quant, chunk, context, device=0):
+    import hashlib
+    hc, specs = dsk.sakusun_from_config(cfg, quant=quant, max_seq_len=context, chunk=chunk)
+    m = dsk.Model(hc, 0, 1, device, layers=specs)
+    dev = torch.device("cuda", device)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def up(name, shape, kind="mat"):
+        torch.manual_seed(int(hashlib.md5(name.encode()).hexdigest()[:8], 16))
+        if kind == "mat":
+            t = torch.randn(*shape, device=dev) * (shape[-1] ** -0.5)
+        elif kind == "embed":
+            t = torch.randn(*shape, device=dev)
+        elif kind == "norm":
+            t = 1.0 + 0.1 * torch.randn(*shape, device=dev)
+        elif kind == "one":
+            t = torch.full((1,), 0.8, device=dev)
+        else:
+            t = 0.1 * torch.randn(*shape, device=dev)
+        t = t.to(torch.bfloat16).contiguous()
+        m.upload_device(name, "BF16", shape, t.data_ptr(), t.numel() * 2)
+        torch.cuda.synchronize()
+
+    up("embed", (V, W), "embed"); up("bigram", (cfg["embedding"]["bigram"]["buckets"] + 1, W), "embed"); up("head", (V, W)); up("final.norm", (), "one")
+    taps = cfg["canon"]["taps"]
+    for i, lc in enumerate(cfg["layers"]):
+        p, mx, ff = f"l{i}.", lc["mixer"], lc["mlp"]["ff"]
+        for n in ("1", "2"):
+            up(p + "norm" + n, (), "one"); up(p + "ls" + n, (W,), "norm"); up(p + "canon" + n, (W, taps), "small")
+            up(p + "rg" + n, (W, W)); up(p + "rg" + n + ".b", (W,), "small")
+        if lc["type"] == "attention":
+            H, G, D, Vd = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+            up(p + "mix.q", (H * D, W)); up(p + "mix.k", (G * D, W)); up(p + "mix.v", (G * Vd, W))
+            up(p + "mix.q.b", (H * D,), "small"); up(p + "mix.k.b", (G * D,), "small"); up(p + "mix.v.b", (G * Vd,), "small")
+            up(p + "mix.q.norm", (H * D,), "norm"); up(p + "mix.k.norm", (G * D,), "norm"); up(p + "mix.rel", (z["rel_rows"], H), "small")
+            up(p + "mix.sink", (H,), "small"); up(p + "mix.vmix", (), "one"); up(p + "mix.o", (W, H * Vd))
+        else:
+            H, D, Rd, Vd, R, Q = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"], mx["q_rank"]
+            up(p + "mix.dq", (Q, W)); up(p + "mix.dq.norm", (Q,), "norm"); up(p + "mix.uq", (H * (D + Rd), Q)); up(p + "mix.dkv", (R + Rd, W))
+            up(p + "mix.dkv.norm", (R,), "norm"); up(p + "mix.uk", (H * D, R)); up(p + "mix.uv", (H * Vd, R)); up(p + "mix.g", (H * Vd, W))
+            up(p + "mix.o", (W, H * Vd))
+        up(p + "mlp.gate", (ff, W)); up(p + "mlp.up", (ff, W)); up(p + "mlp.down", (W, ff))
+    m.finalize()
+    return m
+
+
+def sakusun_matrix_elements(cfg, z):
+    """Matrix elements one token multiplies with (projections, gates, feed-forward, head), and the attention's own multiply-adds
+    per token at the mean number of visible keys of a prompt of `window` x 2 tokens."""
+    W, n, att = cfg["width"], cfg["width"] * cfg["vocab"], 0.0
+    for lc in cfg["layers"]:
+        mx = lc["mixer"]
+        n += 2 * W * W + 3 * lc["mlp"]["ff"] * W
+        if lc["type"] == "attention":
+            H, G, D, Vd = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+            n += (H * D + G * D + G * Vd) * W + W * H * Vd
+            att += H * (D + Vd) * (z["window"] / 2.0)
+        else:
+            H, D, Rd, Vd, R, Q = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"], mx["q_rank"]
+            n += (Q + R + Rd) * W + H * (D + Rd) * Q + H * (D + Vd) * R + 2 * H * Vd * W
+            att += H * (D + Rd + Vd) * z["window"]
+    return n, att
+
+
+def run_sakusun(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log):
+    """A Sakusun size and the closest model of the framework (Rutulix) at equal size."""
+    z = SIZES[name]
+    cfg = sakusun_config(z)
+    t0 = time.time()
+    m = mint_sakusun(dsk, torch, cfg, z, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    mat, att = sakusun_matrix_elements(cfg, z)
+    res = [measure_layer_list(m, f"Sakusun {name}", z["vocab"], 2.0 * mat, hbm, tfl, prompt_len, gen, chunk, log,
+                              {"layers": len(z["pattern"]), "width": z["width"], "attention_flops_per_token_fp32": 2.0 * att})]
+    m.close()
+    zr = closest_rutulix(z)
+    cfgr = rutulix_config(zr)
+    t0 = time.time()
+    m = mint_rutulix(dsk, torch, cfgr, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/closest Rutulix/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    mat, att = rutulix_matrix_elements(cfgr, zr)
+    res.append(measure_layer_list(m, f"Rutulix layers at {name}", z["vocab"], 2.0 * mat, hbm, tfl, prompt_len, gen, chunk, log,
+                                  {"layer_runs": rutulix_runs(zr), "width": z["width"], "attention_flops_per_token_fp32": 2.0 * att}))
+    m.close()
+    return res
 
 
 def rutulix_config(z):
@@ -250,6 +361,9 @@ def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_l
         z = SIZES[name]
         if z.get("design") == "Rutulix":
             out["results"] += run_rutulix(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log)
+            continue
+        if z.get("design") == "Sakusun":
+            out["results"] += run_sakusun(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log)
             continue
         cfg = desarax_config(z)
         for quant in ("bf16",):

@@ -93,9 +93,10 @@ def attention_step(W, p, mx, u, pos, cache, eps, v_first, mixes):
     js = [j for j in range(pos + 1) if sees(mx.get("mask"), pos, j)]
     out = np.zeros((H, Vd))
     cap = mx.get("softcap")
+    keys, vals = np.array([cache["k"][j] for j in js]), np.array([cache["v"][j] for j in js])      # [visible, G, .]
     for h in range(H):
         g = h // (H // G)
-        s = np.array([mx["scale"] * float(q[h] @ cache["k"][j][g]) for j in js])
+        s = mx["scale"] * (keys[:, g] @ q[h])
         if cap:
             s = cap * np.tanh(s / cap)
         if "bias_max" in mx:
@@ -105,8 +106,7 @@ def attention_step(W, p, mx, u, pos, cache, eps, v_first, mixes):
         m = max(float(s.max()), sink)
         e = np.exp(s - m)
         pr = e / (e.sum() + math.exp(sink - m))
-        for n, j in enumerate(js):
-            out[h] += pr[n] * cache["v"][j][g]
+        out[h] = pr @ vals[:, g]
     return W[p + "o"] @ out.reshape(-1), v
 
 
@@ -132,13 +132,12 @@ def latent_attention_step(W, p, mx, u, pos, cache, eps):
     cache["kr"].append(rotate(dkv[R:], mx["rot"], pos))
     uk, uv = W[p + "uk"].reshape(H, D, R), W[p + "uv"].reshape(H, Vd, R)
     out = np.zeros((H, Vd))
+    lat, kr = np.array(cache["c"]), np.array(cache["kr"])               # [pos + 1, R], [pos + 1, Rd]
     for h in range(H):
         qr = rotate(q[h, D:], mx["rot"], pos)
-        s = np.array([mx["scale"] * (float(q[h, :D] @ (uk[h] @ cache["c"][j])) + float(qr @ cache["kr"][j])) for j in range(pos + 1)])
+        s = mx["scale"] * ((lat @ uk[h].T) @ q[h, :D] + kr @ qr)           # plain keys of head h: uk[h] c_j
         e = np.exp(s - s.max())
-        pr = e / e.sum()
-        for j in range(pos + 1):
-            out[h] += pr[j] * (uv[h] @ cache["c"][j])
+        out[h] = (e / e.sum()) @ (lat @ uv[h].T)
     return W[p + "o"] @ (out.reshape(-1) * logistic(W[p + "g"] @ u))
 
 
@@ -267,6 +266,10 @@ def random_weights(cfg, seed=0):
     return W
 
 
+def write(dirname, cfg, W):
+    return write_checkpoint(dirname, public_config(cfg), W)
+
+
 def public_config(cfg):
     """The config.json form: without the helper key that only sizes the test's distance table."""
     out = dict(cfg)
@@ -279,14 +282,20 @@ def public_config(cfg):
 
 
 def att(heads=3, kv_heads=None, dim=8, vdim=8, size=6, keep_first=2, scale=0.3, softcap=20.0, bias_max=24, rel_rows=8, v_mix=True, ff=None):
-    mx = {"heads": heads, "kv_heads": kv_heads or heads, "dim": dim, "vdim": vdim, "scale": scale, "softcap": softcap, "bias_max": bias_max,
-          "rel_rows": rel_rows, "mask": {"size": size, "keep_first": keep_first}, "v_mix": v_mix}
+    """One attention layer of a config; None for size / softcap / bias_max leaves that key out (plain causal / no cap / no bias)."""
+    mx = {"heads": heads, "kv_heads": kv_heads or heads, "dim": dim, "vdim": vdim, "scale": scale, "v_mix": v_mix}
+    if size is not None:
+        mx["mask"] = {"size": size, "keep_first": keep_first}
+    if softcap is not None:
+        mx["softcap"] = softcap
+    if bias_max is not None:
+        mx.update(bias_max=bias_max, rel_rows=rel_rows)
     return {"type": "attention", "mixer": mx, "mlp": {"kind": "dense", "ff": ff} if ff else None}
 
 
-def lat(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=12, q_rank=10, scale=0.3, base=100.0, ff=None):
+def lat(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=12, q_rank=10, scale=0.3, base=100.0, dims=None, ff=None):
     mx = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale,
-          "rot": {"dims": rot_dim, "base": base}}
+          "rot": {"dims": rot_dim if dims is None else dims, "base": base}}
     return {"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": ff} if ff else None}
 
 

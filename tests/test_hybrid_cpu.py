@@ -137,3 +137,58 @@ def test_rutulix_oracle_invariants(ro):
     d1 = (ro.rotate_heads(v, 2, 6, rot, 5) * ro.rotate_heads(w, 2, 6, rot, 2)).sum()
     d2 = (ro.rotate_heads(v, 2, 6, rot, 9) * ro.rotate_heads(w, 2, 6, rot, 6)).sum()
     assert abs(d1 - d2) < 1e-9
+
+
+# ---- the Sakusun design ---------------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def so():
+    import sakusun_oracle
+    return sakusun_oracle
+
+
+def test_sakusun_config_to_layer_specs(so):
+    import dsk
+    cfg = so.public_config(so.small_config())
+    hc, specs = dsk.ARCHITECTURES[cfg["architecture"]](cfg, quant="bf16", max_seq_len=77, chunk=16)
+    assert (hc.dim, hc.vocab_size, hc.n_layers, hc.max_seq_len, hc.chunk, hc.side_dim, hc.loop_times) == (44, 61, 5, 77, 16, 0, 0)
+    assert (hc.block, hc.norm_kind, hc.norm_scalar, hc.tie_head, hc.canon_taps, hc.res_gate, hc.layer_scale) == (dsk.BLOCK_POST, dsk.NORM_RMS, 1, 0, 4, 1, 1)
+    assert (hc.bigram_buckets, hc.bigram_mul_prev, hc.bigram_mul_cur) == (37, 5, 3) and abs(hc.embed_scale - 0.5) < 1e-7
+    a, b, c, d, e = specs
+    assert (a.mixer, a.att_heads, a.att_kv_heads, a.att_dim, a.att_vdim, a.att_mask, a.att_window, a.att_keep_first) == (dsk.MIX_GQA, 6, 2, 10, 6, dsk.MASK_WINDOW, 7, 3)
+    assert (a.att_value_proj, a.att_bias, a.att_sink, a.att_vmix, a.att_talk, a.att_rel_max, a.rot_dims) == (1, 1, 1, 1, 0, 20, 0) and abs(a.att_softcap - 15.0) < 1e-6
+    assert (a.ff_kind, a.ff_hidden, a.ff_act) == (dsk.FF_DENSE, 28, dsk.ACT_GEGLU)
+    assert (b.mixer, b.att_heads, b.att_dim, b.att_rot_dim, b.att_vdim, b.att_kv_rank, b.att_q_rank, b.att_out_gate, b.rot_dims) == (dsk.MIX_MLA, 3, 12, 6, 10, 14, 9, 1, 6)
+    assert b.att_window == 1 << 30 and b.ff_kind == dsk.FF_NONE and abs(b.rot_base - 500.0) < 1e-3
+    assert c.att_kv_heads == 1 and c.att_keep_first == 0 and e.att_vmix == 0 and d.att_rot_dim == 8
+    m = cfg["layers"][0]["mixer"]
+    del m["softcap"], m["bias_max"], m["mask"], m["kv_heads"]
+    a = dsk.sakusun_from_config(cfg)[1][0]
+    assert (a.att_softcap, a.att_rel_max, a.att_window, a.att_keep_first, a.att_kv_heads) == (0.0, 0, 1 << 30, 0, 6)
+    cfg["layers"][1]["type"] = "mamba2"
+    with pytest.raises(dsk.DskError):
+        dsk.sakusun_from_config(cfg)
+
+
+def test_sakusun_oracle_invariants(so):
+    """(1) window with kept first positions; (2) distance buckets: one per distance below half, logarithmic steps above, the last
+    one from the limit on; (3) a sequence fed token by token equals the whole; (4) the input convolution's carry; (5) rotation
+    depends on the position difference only and leaves the entries beyond `dims` alone."""
+    mask = {"size": 4, "keep_first": 2}
+    assert [j for j in range(12) if so.sees(mask, 9, j)] == [0, 1, 6, 7, 8, 9]
+    assert [j for j in range(12) if so.sees(None, 3, j)] == [0, 1, 2, 3]
+    bk = [so.rel_bucket(n, 32, 120) for n in range(0, 400)]
+    assert bk[:16] == list(range(16)) and bk[16] == 16 and bk[119] == 31 and bk[120] == 31 and bk[399] == 31 and all(x <= y for x, y in zip(bk, bk[1:]))
+    cfg = so.small_config()
+    W = so.random_weights(cfg, 5)
+    toks = np.arange(20) % 61
+    whole = so.run(cfg, W, toks)[0]
+    seq = so.Sequence(cfg, W)
+    assert np.allclose(np.array([seq.feed(int(t)) for t in toks]), whole, rtol=0, atol=1e-12)
+    w = np.random.RandomState(0).randn(5, 3)
+    xs = [np.random.RandomState(i).randn(5) for i in range(4)]
+    u = so.input_conv(w, [xs[1], xs[2]], xs[3])
+    assert np.allclose(u, xs[3] + w[:, 0] * xs[1] + w[:, 1] * xs[2] + w[:, 2] * xs[3])
+    rot = {"dims": 4, "base": 50.0}
+    v, k = np.random.RandomState(1).randn(6), np.random.RandomState(2).randn(6)
+    assert abs(so.rotate(v, rot, 5) @ so.rotate(k, rot, 2) - so.rotate(v, rot, 9) @ so.rotate(k, rot, 6)) < 1e-9
+    assert np.array_equal(so.rotate(v, rot, 7)[4:], v[4:])
