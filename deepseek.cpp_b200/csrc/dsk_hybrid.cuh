@@ -526,6 +526,61 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   }
 }
 
+// Decode-sized steps (T <= kCloseOpenTokens) of post-norm blocks: the end of one sublayer and the start of the next in one CTA,
+//   x_t += alpha * rms(y_t) * cw   (cw: norm weight x layer scale);   u_t = x_t + conv(x)_t   with the ring handled as in canon_conv.
+// A thread owns channels tid, tid + blockDim, .. over all tokens of the step; the row sums of squares are reduced first.
+constexpr int kCloseOpenTokens = 8;
+__global__ void __launch_bounds__(1024) close_open_small(const float* __restrict__ y, const float* __restrict__ cw, float alpha, float eps,
+                                                         float* __restrict__ x, int ld, const float* __restrict__ w, float* __restrict__ hist,
+                                                         float* __restrict__ u, int T, int ch, int taps, const int* __restrict__ ctl) {
+  __shared__ float red[33];
+  float sc[kCloseOpenTokens];
+#pragma unroll
+  for (int t = 0; t < kCloseOpenTokens; t++) {
+    if (t < T) {
+      float ss = 0.f;
+      for (int c = threadIdx.x; c < ch; c += blockDim.x) { const float v = y[(size_t)t * ld + c]; ss = fmaf(v, v, ss); }
+      sc[t] = 1.f / sqrtf(block_sum(ss, red) / (float)ch + eps);
+    } else sc[t] = 0.f;
+  }
+  const int pos0 = ctl[0], back = taps - 1;
+  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
+    float wk[kCanonMaxTaps], win[kCanonMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps; j++) wk[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+      const int p = pos0 - back + j;
+      win[j] = (j < back && p >= 0) ? hist[(size_t)(p % back) * ch + c] : 0.f;
+    }
+    const float cwc = cw[c];
+#pragma unroll
+    for (int t = 0; t < kCloseOpenTokens; t++) {
+      if (t < T) {
+        const float cur = fmaf(alpha, y[(size_t)t * ld + c] * sc[t] * cwc, x[(size_t)t * ld + c]);
+        x[(size_t)t * ld + c] = cur;
+        float acc = cur;
+#pragma unroll
+        for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j < back) acc = fmaf(wk[j], win[j], acc);
+#pragma unroll
+        for (int j = 0; j < kCanonMaxTaps; j++) if (j == back) acc = fmaf(wk[j], cur, acc);
+        u[(size_t)t * ld + c] = acc;
+#pragma unroll
+        for (int j = 0; j < kCanonMaxTaps - 2; j++) if (j + 1 < back) win[j] = win[j + 1];
+#pragma unroll
+        for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j == back - 1) win[j] = cur;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+      if (j < back) {
+        const int p = pos0 + T - back + j;
+        if (p >= 0) hist[(size_t)(p % back) * ch + c] = win[j];
+      }
+    }
+  }
+}
+
 template <typename WT> struct WVec;
 template <> struct WVec<float> {
   static constexpr int N = 4;
@@ -828,9 +883,24 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
   for (int k = 0; k < RV; k++) acc[k] = 0.f;
   for (int j0 = lo; j0 <= hi; j0 += 32) {
     __syncthreads();
-    for (int e = threadIdx.x; e < 32 * R; e += blockDim.x) {
-      const int jj = e / R, r = e - jj * R, j = j0 + jj;
-      ks[jj * (R + 1) + r] = j <= hi ? to_f<CT>(cache[(size_t)(j % ring) * R + r]) : 0.f;
+    // warp w stages the tile's rows w, w + 8, ..: one ring row index per row, then (fp32 caches of a width that is a multiple of 4)
+    // 16-byte loads with all of a lane's loads in flight before the first store
+    for (int jj = w; jj < 32; jj += 8) {
+      const int j = j0 + jj;
+      float* dst = ks + jj * (R + 1);
+      if (j > hi) { for (int r = lane; r < R; r += 32) dst[r] = 0.f; continue; }
+      const CT* src = cache + (size_t)(j % ring) * R;
+      if (sizeof(CT) == 4 && (R & 3) == 0) {
+        const float4* s4 = reinterpret_cast<const float4*>(src);
+        const int n4 = R >> 2;
+#pragma unroll 8
+        for (int q = lane; q < n4; q += 32) {
+          const float4 v = s4[q];
+          dst[4 * q] = v.x; dst[4 * q + 1] = v.y; dst[4 * q + 2] = v.z; dst[4 * q + 3] = v.w;
+        }
+      } else {
+        for (int r = lane; r < R; r += 32) dst[r] = to_f<CT>(src[r]);
+      }
     }
     __syncthreads();
     const int j = j0 + lane;
@@ -884,8 +954,9 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
   }
 }
 
-// merges the NS partial softmax results of one (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s
-__global__ void latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS) {
+// merges the NS partial softmax results of one (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s.
+// Grid (token x head, blocks of 128 columns): a thread owns one column and reads its NS partial values with independent loads.
+__global__ void __launch_bounds__(128) latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS) {
   __shared__ float wts[64], ms[64];   // NS <= 64 (kAttnSplitMax)
   const size_t th = blockIdx.x;
   const float* pp = part + th * NS * (R + 2);
@@ -898,11 +969,17 @@ __global__ void latent_swa_merge(const float* __restrict__ part, float* __restri
   float l = 0.f;
   for (int s = 0; s < NS; s++) l = fmaf(wts[s], pp[(size_t)s * (R + 2) + 1], l);
   const float inv = 1.f / l;
-  for (int r = threadIdx.x; r < R; r += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < NS; s++) a = fmaf(wts[s], pp[(size_t)s * (R + 2) + 2 + r], a);
-    out[th * R + r] = a * inv;
+  const int r = blockIdx.y * 128 + threadIdx.x;
+  if (r >= R) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int s = 0;
+  for (; s + 4 <= NS; s += 4) {
+    const float v0 = pp[(size_t)s * (R + 2) + 2 + r], v1 = pp[(size_t)(s + 1) * (R + 2) + 2 + r];
+    const float v2 = pp[(size_t)(s + 2) * (R + 2) + 2 + r], v3 = pp[(size_t)(s + 3) * (R + 2) + 2 + r];
+    a0 = fmaf(wts[s], v0, a0); a1 = fmaf(wts[s + 1], v1, a1); a2 = fmaf(wts[s + 2], v2, a2); a3 = fmaf(wts[s + 3], v3, a3);
   }
+  for (; s < NS; s++) a0 = fmaf(wts[s], pp[(size_t)s * (R + 2) + 2 + r], a0);
+  out[th * R + r] = ((a0 + a1) + (a2 + a3)) * inv;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

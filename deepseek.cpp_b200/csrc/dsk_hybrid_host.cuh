@@ -690,7 +690,7 @@ static int launches_per_token(const dsk_model* m) {
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.canon_taps > 0 ? 1 : 0) + (M->c.res_gate ? 1 : 0));   // convolution, gate, closing norm
+    if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0)) + (&R == &M->runs[0] && M->c.canon_taps > 0 ? 1 : 0);   // gate, closing norm + next convolution in one
     else if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
     else n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
     if (s.mixer == DSK_MIX_GQA) n += s.att_value_proj ? 5 : 6;   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, o
@@ -994,7 +994,7 @@ static void launch_attn(const float* qa, const float* cache, float* out, int T, 
   else if (R <= 256) latent_swa_attn<float, 8><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
   else if (R <= 512) latent_swa_attn<float, 16><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
   else latent_swa_attn<float, 32><<<grid, 256, smem, st>>>(qa, cache, out, T, H, R, ctl, mask, window, ring, scale, TQ, NS, part);
-  if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(part, out, R, NS);
+  if (NS > 1) latent_swa_merge<<<dim3((unsigned)(T * H), (unsigned)((R + 127) / 128)), 128, 0, st>>>(part, out, R, NS);
 }
 
 // LM head on the wanted rows [first, first + count) of the chunk whose normalised rows are in S->h -> S->logits [count][vocab]
@@ -1075,8 +1075,22 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       }
       norm_rows(c, S, S->y, close_w, S->x, T, 1, mult, st);
     };
+    // decode-sized steps: the closing norm and the next sublayer's input convolution as one kernel (not while the stream is recorded);
+    // next_taps / next_ring: the convolution that follows (the feed-forward's, or the next layer's mixer's)
+    const bool small_post = post && c.canon_taps > 0 && T <= kCloseOpenTokens && !trace;
+    auto close_open = [&](const HTensor& rg, const float* rg_b, const float* close_w, const float* next_taps, float* next_ring) {
+      if (c.res_gate) {
+        GemmP G = gp(S->x, W, rg.p, W, S->y, W, T, W, W);
+        G.bias = rg_b;
+        linear(S, bf, HEPI_SIGMUL, G, 1, st);
+      }
+      close_open_small<<<1, std::min(1024, (W + 31) / 32 * 32), 0, st>>>(S->y, close_w, mult, c.norm_eps, S->x, W, next_taps, next_ring, S->h, T, W, c.canon_taps, S->d_ctl);
+      S->launches++;
+    };
+    auto ring_of = [&](size_t run_i, int which) { return S->L[run_i].canon ? S->L[run_i].canon + (size_t)which * (c.canon_taps - 1) * W : nullptr; };
+    const bool has_next = ri + 1 < M->runs.size();
     const float* hin = S->h;   // what the mixer reads
-    if (post) hin = open_post(L.canon1, 0);
+    if (post) { if (!h_ready) hin = open_post(L.canon1, 0); }
     else if (!h_ready) {
       if (run.pass >= 0) {   // a pass of the layer loop opens with its own vector added to the residual stream
         add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
@@ -1152,7 +1166,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, L.ring) + keep + 31) / 32, kAttnSplitMax));
         gqa_attn<<<dim3((unsigned)T, (unsigned)NS), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
             S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, NS, S->part, sm);
-        if (NS > 1) latent_swa_merge<<<T * H, 128, 0, st>>>(S->part, S->b3, V, NS);
+        if (NS > 1) latent_swa_merge<<<dim3((unsigned)(T * H), (unsigned)((V + 127) / 128)), 128, 0, st>>>(S->part, S->b3, V, NS);
         S->launches += NS > 1 ? 2 : 1;
         MK("att.decode");
       }
@@ -1303,9 +1317,13 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
     }
-    if (post) {   // the mixer's result closes; the feed-forward opens on the new stream
-      close_post(L.rg1, L.rg1_b, L.close1);
-      if (sp.ff_kind != DSK_FF_NONE) hin = open_post(L.canon2, 1);
+    if (post) {   // the mixer's result closes; the feed-forward (or, without one, the next layer's mixer) opens on the new stream
+      if (small_post && sp.ff_kind != DSK_FF_NONE) { close_open(L.rg1, L.rg1_b, L.close1, L.canon2, ring_of(ri, 1)); hin = S->h; }
+      else if (small_post && has_next) { close_open(L.rg1, L.rg1_b, L.close1, M->L[M->runs[ri + 1].layer].canon1, ring_of(ri + 1, 0)); h_ready = true; }
+      else {
+        close_post(L.rg1, L.rg1_b, L.close1);
+        if (sp.ff_kind != DSK_FF_NONE) hin = open_post(L.canon2, 1);
+      }
       MK("norm");
     }
     if (sandwich) {   // x += norm1b(mixer output); the feed-forward then reads norm2 of the new x
@@ -1378,7 +1396,8 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       MK("norm");
     }
     if (post && sp.ff_kind != DSK_FF_NONE) {
-      close_post(L.rg2, L.rg2_b, L.close2);
+      if (small_post && has_next) { close_open(L.rg2, L.rg2_b, L.close2, M->L[M->runs[ri + 1].layer].canon1, ring_of(ri + 1, 0)); h_ready = true; }
+      else close_post(L.rg2, L.rg2_b, L.close2);
       MK("norm");
     }
     if (c.side_dim > 0) {
