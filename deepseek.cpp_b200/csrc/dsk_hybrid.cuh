@@ -526,57 +526,64 @@ __global__ void __launch_bounds__(256) gemm_mma(const GemmP P) {
   }
 }
 
-// Decode-sized steps (T <= kCloseOpenTokens) of post-norm blocks: the end of one sublayer and the start of the next in one CTA,
+// Decode-sized steps (T <= kCloseOpenTokens) of post-norm blocks: the end of one sublayer and the start of the next in one kernel,
 //   x_t += alpha * rms(y_t) * cw   (cw: norm weight x layer scale);   u_t = x_t + conv(x)_t   with the ring handled as in canon_conv.
-// A thread owns channels tid, tid + blockDim, .. over all tokens of the step; the row sums of squares are reduced first.
+// A CTA owns 128 channels over all tokens of the step; every CTA sums the squares of the whole rows of y itself (they are a few
+// KB and sit in L2), so no CTA waits for another.
 constexpr int kCloseOpenTokens = 8;
-__global__ void __launch_bounds__(1024) close_open_small(const float* __restrict__ y, const float* __restrict__ cw, float alpha, float eps,
-                                                         float* __restrict__ x, int ld, const float* __restrict__ w, float* __restrict__ hist,
-                                                         float* __restrict__ u, int T, int ch, int taps, const int* __restrict__ ctl) {
+__global__ void __launch_bounds__(128) close_open_small(const float* __restrict__ y, const float* __restrict__ cw, float alpha, float eps,
+                                                        float* __restrict__ x, int ld, const float* __restrict__ w, float* __restrict__ hist,
+                                                        float* __restrict__ u, int T, int ch, int taps, const int* __restrict__ ctl) {
   __shared__ float red[33];
   float sc[kCloseOpenTokens];
 #pragma unroll
   for (int t = 0; t < kCloseOpenTokens; t++) {
     if (t < T) {
-      float ss = 0.f;
-      for (int c = threadIdx.x; c < ch; c += blockDim.x) { const float v = y[(size_t)t * ld + c]; ss = fmaf(v, v, ss); }
-      sc[t] = 1.f / sqrtf(block_sum(ss, red) / (float)ch + eps);
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float* yr = y + (size_t)t * ld;
+      int c = threadIdx.x;
+      for (; c + 3 * 128 < ch; c += 4 * 128) {   // four independent loads per round
+        const float v0 = yr[c], v1 = yr[c + 128], v2 = yr[c + 256], v3 = yr[c + 384];
+        s0 = fmaf(v0, v0, s0); s1 = fmaf(v1, v1, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+      }
+      for (; c < ch; c += 128) { const float v = yr[c]; s0 = fmaf(v, v, s0); }
+      sc[t] = 1.f / sqrtf(block_sum((s0 + s1) + (s2 + s3), red) / (float)ch + eps);
     } else sc[t] = 0.f;
   }
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= ch) return;
   const int pos0 = ctl[0], back = taps - 1;
-  for (int c = threadIdx.x; c < ch; c += blockDim.x) {
-    float wk[kCanonMaxTaps], win[kCanonMaxTaps];
+  float wk[kCanonMaxTaps], win[kCanonMaxTaps];
 #pragma unroll
-    for (int j = 0; j < kCanonMaxTaps; j++) wk[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+  for (int j = 0; j < kCanonMaxTaps; j++) wk[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
 #pragma unroll
-    for (int j = 0; j < kCanonMaxTaps - 1; j++) {
-      const int p = pos0 - back + j;
-      win[j] = (j < back && p >= 0) ? hist[(size_t)(p % back) * ch + c] : 0.f;
+  for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+    const int p = pos0 - back + j;
+    win[j] = (j < back && p >= 0) ? hist[(size_t)(p % back) * ch + c] : 0.f;
+  }
+  const float cwc = cw[c];
+#pragma unroll
+  for (int t = 0; t < kCloseOpenTokens; t++) {
+    if (t < T) {
+      const float cur = fmaf(alpha, y[(size_t)t * ld + c] * sc[t] * cwc, x[(size_t)t * ld + c]);
+      x[(size_t)t * ld + c] = cur;
+      float acc = cur;
+#pragma unroll
+      for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j < back) acc = fmaf(wk[j], win[j], acc);
+#pragma unroll
+      for (int j = 0; j < kCanonMaxTaps; j++) if (j == back) acc = fmaf(wk[j], cur, acc);
+      u[(size_t)t * ld + c] = acc;
+#pragma unroll
+      for (int j = 0; j < kCanonMaxTaps - 2; j++) if (j + 1 < back) win[j] = win[j + 1];
+#pragma unroll
+      for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j == back - 1) win[j] = cur;
     }
-    const float cwc = cw[c];
+  }
 #pragma unroll
-    for (int t = 0; t < kCloseOpenTokens; t++) {
-      if (t < T) {
-        const float cur = fmaf(alpha, y[(size_t)t * ld + c] * sc[t] * cwc, x[(size_t)t * ld + c]);
-        x[(size_t)t * ld + c] = cur;
-        float acc = cur;
-#pragma unroll
-        for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j < back) acc = fmaf(wk[j], win[j], acc);
-#pragma unroll
-        for (int j = 0; j < kCanonMaxTaps; j++) if (j == back) acc = fmaf(wk[j], cur, acc);
-        u[(size_t)t * ld + c] = acc;
-#pragma unroll
-        for (int j = 0; j < kCanonMaxTaps - 2; j++) if (j + 1 < back) win[j] = win[j + 1];
-#pragma unroll
-        for (int j = 0; j < kCanonMaxTaps - 1; j++) if (j == back - 1) win[j] = cur;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < kCanonMaxTaps - 1; j++) {
-      if (j < back) {
-        const int p = pos0 + T - back + j;
-        if (p >= 0) hist[(size_t)(p % back) * ch + c] = win[j];
-      }
+  for (int j = 0; j < kCanonMaxTaps - 1; j++) {
+    if (j < back) {
+      const int p = pos0 + T - back + j;
+      if (p >= 0) hist[(size_t)(p % back) * ch + c] = win[j];
     }
   }
 }

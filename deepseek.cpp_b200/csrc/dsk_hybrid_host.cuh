@@ -1084,7 +1084,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         G.bias = rg_b;
         linear(S, bf, HEPI_SIGMUL, G, 1, st);
       }
-      close_open_small<<<1, std::min(1024, (W + 31) / 32 * 32), 0, st>>>(S->y, close_w, mult, c.norm_eps, S->x, W, next_taps, next_ring, S->h, T, W, c.canon_taps, S->d_ctl);
+      close_open_small<<<(W + 127) / 128, 128, 0, st>>>(S->y, close_w, mult, c.norm_eps, S->x, W, next_taps, next_ring, S->h, T, W, c.canon_taps, S->d_ctl);
       S->launches++;
     };
     auto ring_of = [&](size_t run_i, int which) { return S->L[run_i].canon ? S->L[run_i].canon + (size_t)which * (c.canon_taps - 1) * W : nullptr; };
