@@ -36,14 +36,14 @@ SIZES = {
 
 
 def sakusun_config(z):
-    att = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5, "softcap": 50.0,
+    att = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5, "softcap": 30.0,
            "bias_max": z["rel_max"], "mask": {"size": z["window"], "keep_first": z["keep"]}, "v_mix": True}
     lat = {"heads": z["att_heads"], "dim": z["lat_dim"], "rot_dim": z["rot"], "vdim": z["lat_dim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
            "scale": (z["lat_dim"] + z["rot"]) ** -0.5, "rot": {"dims": z["rot"], "base": 10000.0}}
     layers = [{"type": "attention" if ch == "A" else "latent_attention", "mixer": dict(att if ch == "A" else lat), "mlp": {"kind": "dense", "ff": z["ff"]}}
               for ch in z["pattern"]]
-    return {"architecture": "Sakusun", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]},
-            "embedding": {"scale": 0.5, "bigram": {"buckets": z["buckets"], "mul_prev": 31, "mul_cur": 7}}}
+    return {"architecture": "Sakusun", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5}, "canon": {"taps": z["taps"]},
+            "embedding": {"scale": 0.75, "bigram": {"buckets": z["buckets"], "mul_prev": 53, "mul_cur": 11}}}
 
 
 def closest_rutulix(z):

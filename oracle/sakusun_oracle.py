@@ -299,7 +299,7 @@ def lat(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=12, q_rank=10, scale=0.3, bas
     return {"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": ff} if ff else None}
 
 
-def model_config(layers, width=40, vocab=53, taps=3, eps=1e-5, emb_scale=0.5, buckets=37, mul_prev=5, mul_cur=3):
+def model_config(layers, width=40, vocab=53, taps=3, eps=1e-5, emb_scale=0.75, buckets=37, mul_prev=5, mul_cur=3):
     return {"architecture": "Sakusun", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": eps}, "canon": {"taps": taps},
             "embedding": {"scale": emb_scale, "bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}}}
 

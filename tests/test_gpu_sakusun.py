@@ -520,7 +520,7 @@ def random_design(seed):
                                  vdim=int(rng.choice([2, 5, 8])), kv_rank=int(rng.choice([3, 8, 17])), q_rank=int(rng.choice([2, 9, 20])),
                                  scale=float(rng.uniform(0.1, 0.6)), base=float(rng.choice([10.0, 1000.0, 50000.0])), ff=ff))
     return so.model_config(layers, width=int(rng.choice([8, 20, 36, 50])), vocab=int(rng.randint(5, 90)), taps=int(rng.choice([1, 2, 3, 4, 6])),
-                           eps=float(rng.choice([1e-6, 1e-5, 1e-3])), emb_scale=float(rng.choice([0.25, 1.0, 3.0])), buckets=int(rng.choice([1, 7, 64, 1021])),
+                           eps=float(rng.choice([1e-6, 1e-5, 1e-3])), emb_scale=float(rng.choice([0.25, 1.0, 3.0])), buckets=int(rng.choice([1, 7, 64, 1013])),
                            mul_prev=int(rng.randint(1, 100)), mul_cur=int(rng.randint(1, 100)))
 
 

@@ -152,7 +152,7 @@ def test_sakusun_config_to_layer_specs(so):
     hc, specs = dsk.ARCHITECTURES[cfg["architecture"]](cfg, quant="bf16", max_seq_len=77, chunk=16)
     assert (hc.dim, hc.vocab_size, hc.n_layers, hc.max_seq_len, hc.chunk, hc.side_dim, hc.loop_times) == (44, 61, 5, 77, 16, 0, 0)
     assert (hc.block, hc.norm_kind, hc.norm_scalar, hc.tie_head, hc.canon_taps, hc.res_gate, hc.layer_scale) == (dsk.BLOCK_POST, dsk.NORM_RMS, 1, 0, 4, 1, 1)
-    assert (hc.bigram_buckets, hc.bigram_mul_prev, hc.bigram_mul_cur) == (37, 5, 3) and abs(hc.embed_scale - 0.5) < 1e-7
+    assert (hc.bigram_buckets, hc.bigram_mul_prev, hc.bigram_mul_cur) == (37, 5, 3) and abs(hc.embed_scale - 0.75) < 1e-7
     a, b, c, d, e = specs
     assert (a.mixer, a.att_heads, a.att_kv_heads, a.att_dim, a.att_vdim, a.att_mask, a.att_window, a.att_keep_first) == (dsk.MIX_GQA, 6, 2, 10, 6, dsk.MASK_WINDOW, 7, 3)
     assert (a.att_value_proj, a.att_bias, a.att_sink, a.att_vmix, a.att_talk, a.att_rel_max, a.rot_dims) == (1, 1, 1, 1, 0, 20, 0) and abs(a.att_softcap - 15.0) < 1e-6
@@ -176,8 +176,8 @@ def test_sakusun_oracle_invariants(so):
     mask = {"size": 4, "keep_first": 2}
     assert [j for j in range(12) if so.sees(mask, 9, j)] == [0, 1, 6, 7, 8, 9]
     assert [j for j in range(12) if so.sees(None, 3, j)] == [0, 1, 2, 3]
-    bk = [so.rel_bucket(n, 32, 120) for n in range(0, 400)]
-    assert bk[:16] == list(range(16)) and bk[16] == 16 and bk[119] == 31 and bk[120] == 31 and bk[399] == 31 and all(x <= y for x, y in zip(bk, bk[1:]))
+    bk = [so.rel_bucket(n, 16, 100) for n in range(0, 400)]
+    assert bk[:8] == list(range(8)) and bk[8] == 8 and bk[99] == 15 and bk[100] == 15 and bk[399] == 15 and all(x <= y for x, y in zip(bk, bk[1:]))
     cfg = so.small_config()
     W = so.random_weights(cfg, 5)
     toks = np.arange(20) % 61
