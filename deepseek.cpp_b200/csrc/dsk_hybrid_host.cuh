@@ -487,6 +487,7 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       }
       if (k == "sink" && s.att_sink) return F32(&L.sink, s.att_heads, 0);
       if (k == "vmix" && s.att_vmix) return SCALAR(&L.vmix, &L.have_vmix);
+      if (k == "vmix" || (k == "rel" && s.att_rel_max <= 0)) return 0;   // a checkpoint may carry them for layers that do not use them
       if (k == "q" && !s.att_value_proj) return MAT(L.q, HD, c.dim);
       if (k == "k" && !s.att_value_proj) return MAT(L.kproj, GD, c.dim);
       if (k == "q.norm") return F32(&L.q_norm, HD, 0);
