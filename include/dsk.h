@@ -66,7 +66,9 @@ typedef struct dsk_config {
  * Every layer: h = norm(x) (RMS norm in norm_groups parts); x += residual_mult * (mixer(h) + ff(h)); then, with side_dim > 0,
  * a per-layer token embedding gated by gelu_tanh(side.gate x) is projected, RMS-normed and added (x += residual_mult * ...).
  * (That is DSK_BLOCK_PARALLEL with DSK_NORM_RMS, the Desarax design; the Rutulix design is DSK_BLOCK_SANDWICH with
- * DSK_NORM_LAYER, DSK_MIX_GQA mixers, DSK_FF_DENSE feed-forwards, an untied head and a layer loop.) */
+ * DSK_NORM_LAYER, DSK_MIX_GQA mixers, DSK_FF_DENSE feed-forwards, an untied head and a layer loop; the Sakusun design is
+ * DSK_BLOCK_POST with single-number RMS norms, DSK_MIX_GQA mixers with their switches on or DSK_MIX_MLA mixers, gated
+ * DSK_FF_DENSE feed-forwards, a scaled embedding plus bigram table and an untied head.) */
 enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2, DSK_MIX_MLA = 3 };
 enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1, DSK_FF_DENSE = 2 };
 enum { DSK_MASK_WINDOW = 0,   /* position i sees j with 0 <= i - j < att_window */
