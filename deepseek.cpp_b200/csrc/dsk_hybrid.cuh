@@ -20,7 +20,10 @@
 //   gqa_attn          softmax attention of grouped query heads over ring caches of keys and values with a window or chunk mask
 //                     and optional mixing of the heads' scores before the softmax (decode-sized steps)
 //   pack_ring_kv, mix_heads, softmax_band   the same attention for portions, between three matrix products
-//   moe_route         sigmoid scores, selection by score + correction, weights = normalised scores x scale
+//   token_shift       h_t + (h_(t-1) - h_t) * mu in front of a mixer, the last row carried from step to step
+//   hgrn2_scan        the gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T silu(q), f = l + (1 - l) sigmoid(.)
+//   moe_route         sigmoid scores, selection by score + correction, weights = normalised scores x scale; or the largest
+//                     logits with a softmax over the chosen ones
 //   moe_plan          groups the (token, slot) pairs of a chunk by expert into row tiles for gemm_tiled
 //   moe_combine       residual += alpha * sum_k w_k y_k (or stored, when a norm follows)
 //
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(256) group_rmsnorm(const float* __restrict__ i
 // ---------------------------------------------------------------------------------------------------------------------
 // matrix products
 // ---------------------------------------------------------------------------------------------------------------------
-enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4, HEPI_GEGLU = 5, HEPI_SIGMUL = 6 };
+enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4, HEPI_GEGLU = 5, HEPI_SIGMUL = 6, HEPI_RELU2 = 7 };
 __host__ __device__ constexpr bool epi_dual(int epi) { return epi == HEPI_GLU || epi == HEPI_GEGLU; }   // two weight matrices per output
 
 struct GemmP {
@@ -227,7 +230,8 @@ struct GemmP {
   const int* n_tiles;
   float alpha;             // STORE: C = alpha acc; ADD: C += alpha acc
   float lim;               // GLU: g = min(gate, lim), u = clamp(up, -lim, lim), C = g sigmoid(1.702 g) (u + 1)
-                           // GEGLU: C = gelu_tanh(gate) * up;  SIGMUL: C *= sigmoid(acc) (a gate on what C already holds)
+                           // GEGLU: C = gelu_tanh(gate) * up;  SIGMUL: C *= sigmoid(acc) (a gate on what C already holds);
+                           // RELU2: C = max(acc, 0)^2
   const void* aux;         // GELU_MUL: C = gelu_tanh(acc) * aux[aux_row[row] * aux_ld + aux_off + n]
   const int* aux_row;
   int aux_ld, aux_off;
@@ -243,6 +247,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict_
   else if (EPI == HEPI_XIELU) crow[n] = v > 0.f ? fmaf(P.act_a * v, v, 0.5f * v) : fmaf(P.act_b, expm1f(v) - v, 0.5f * v);
   else if (EPI == HEPI_GEGLU) crow[n] = gelu_tanh_f(v) * v2;
   else if (EPI == HEPI_SIGMUL) crow[n] *= sigmoid_f(v);
+  else if (EPI == HEPI_RELU2) { const float r = fmaxf(v, 0.f); crow[n] = r * r; }
   else if (EPI == HEPI_GLU) {
     const float g = fminf(v, P.lim), u = fminf(fmaxf(v2, -P.lim), P.lim);
     crow[n] = g * sigmoid_f(1.702f * g) * (u + 1.f);
@@ -827,6 +832,120 @@ __global__ void __launch_bounds__(512) ssd_scan(const float* __restrict__ proj, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Token shift in front of a mixer:  h_t = x_t + (x_(t-1) - x_t) * mu  per channel, with x_(-1) = 0 at the start of a sequence.
+// `carry` [ch] holds the last row of the previous step.  Thread = channel, CTA = 128 channels x up to kCanonTokens consecutive
+// tokens.  A step of at most kCanonTokens tokens (one CTA along the tokens) also stores its last row in `carry`, each thread
+// after its own read; longer steps run shift_carry afterwards, because their first CTA reads what the last one would write.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) token_shift(const float* __restrict__ x, int ld, const float* __restrict__ mu, float* __restrict__ carry,
+                                                   float* __restrict__ h, int ldh, int T, int ch, const int* __restrict__ ctl) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= ch) return;
+  const int t0 = blockIdx.y * kCanonTokens, t1 = min(T, t0 + kCanonTokens);
+  float prev = t0 > 0 ? x[(size_t)(t0 - 1) * ld + c] : (ctl[0] > 0 ? carry[c] : 0.f);
+  const float m = mu[c];
+  for (int t = t0; t < t1; t++) {
+    const float cur = x[(size_t)t * ld + c];
+    h[(size_t)t * ldh + c] = fmaf(prev - cur, m, cur);
+    prev = cur;
+  }
+  if (gridDim.y == 1) carry[c] = prev;
+}
+__global__ void shift_carry(const float* __restrict__ x, int ld, float* __restrict__ carry, int T, int ch) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < ch) carry[c] = x[(size_t)(T - 1) * ld + c];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Gated linear recurrence (HGRN2 form) over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens:
+//   f = l + (1 - l) sigmoid(raw_f)   per head and key channel n (l: lower bound);   q = silu(raw_q);
+//   S[n][p] <- f[n] S[n][p] + (1 - f[n]) v[p]   (computed as v + f (S - v));   o[p] = sum_n q[n] S[n][p]
+// proj rows hold [raw_q | raw_f | v] at the given offsets (H * N, H * N, H * P wide); state [H][N][P] fp32.  Thread (pl, s) owns
+// value channel p = p0 + pl and 4 RQ rows n = 4 (s + 8 j) + k of S[:, p] in registers; the eight threads of a channel reduce o with
+// shuffles.  Gates and queries of TB tokens at a time are computed while they are staged, off the sequential path.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int RQ>
+__global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
+                                                  const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ out,
+                                                  int ld_out, int T, int H, int N, int P, int PB, int TB) {
+  extern __shared__ __align__(16) float sm[];
+  const int NP = (N + 3) & ~3;      // staged rows are padded to whole float4s
+  float* s_f = sm;                  // [TB][NP]
+  float* s_q = s_f + TB * NP;       // [TB][NP]
+  float* s_v = s_q + TB * NP;       // [TB][PB]
+  const int h = blockIdx.x, p0 = blockIdx.y * PB;
+  const int tid = threadIdx.x, pl = tid >> 3, s = tid & 7, p = p0 + pl;
+  const bool pok = pl < PB && p < P;
+  float S[RQ][4];
+#pragma unroll
+  for (int j = 0; j < RQ; j++)
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int n = 4 * (s + 8 * j) + k;
+      S[j][k] = (pok && n < N) ? state[((size_t)h * N + n) * P + p] : 0.f;
+    }
+  for (int t0 = 0; t0 < T; t0 += TB) {
+    const int nt = min(TB, T - t0);
+    __syncthreads();
+    for (int base = 0; base < nt * NP; base += 4 * (int)blockDim.x) {   // four elements per thread and pass: eight loads in flight
+      float rf[4], rq[4], lo[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        const int tt = i / NP, n = i - tt * NP;
+        const bool ok = i < nt * NP && n < N;
+        rf[u] = ok ? proj[(size_t)(t0 + tt) * ld + f_off + h * N + n] : 0.f;
+        rq[u] = ok ? proj[(size_t)(t0 + tt) * ld + q_off + h * N + n] : 0.f;
+        lo[u] = ok ? lower[h * N + n] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = base + u * (int)blockDim.x + tid;
+        const int tt = i / NP, n = i - tt * NP;
+        if (i < nt * NP) {
+          const bool ok = n < N;     // padding rows: f = 0, q = 0 (they never reach the output or the stored state)
+          s_f[i] = ok ? fmaf(1.f - lo[u], sigmoid_f(rf[u]), lo[u]) : 0.f;
+          s_q[i] = ok ? silu_f(rq[u]) : 0.f;
+        }
+      }
+    }
+    for (int i = tid; i < nt * PB; i += blockDim.x) {
+      const int tt = i / PB, k = i - tt * PB, pp = p0 + k;
+      s_v[i] = pp < P ? proj[(size_t)(t0 + tt) * ld + v_off + h * P + pp] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float xv = pl < PB ? s_v[tt * PB + pl] : 0.f;
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < RQ; j++) {
+        const int n4 = 4 * (s + 8 * j);
+        if (n4 < NP) {
+          const float4 f = *reinterpret_cast<const float4*>(s_f + tt * NP + n4);
+          const float4 c = *reinterpret_cast<const float4*>(s_q + tt * NP + n4);
+          S[j][0] = fmaf(f.x, S[j][0] - xv, xv); S[j][1] = fmaf(f.y, S[j][1] - xv, xv);
+          S[j][2] = fmaf(f.z, S[j][2] - xv, xv); S[j][3] = fmaf(f.w, S[j][3] - xv, xv);
+          y0 = fmaf(S[j][0], c.x, y0); y1 = fmaf(S[j][1], c.y, y1);
+          y0 = fmaf(S[j][2], c.z, y0); y1 = fmaf(S[j][3], c.w, y1);
+        }
+      }
+      float y = y0 + y1;
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      y += __shfl_xor_sync(0xffffffffu, y, 4);
+      if (s == 0 && pok) out[(size_t)(t0 + tt) * ld_out + h * P + p] = y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < RQ; j++)
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int n = 4 * (s + 8 * j) + k;
+      if (pok && n < N) state[((size_t)h * N + n) * P + p] = S[j][k];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // Sliding-window softmax attention over cached latents with the key up-projection absorbed into the query:
 //   score(i, j) = scale * qa[i][h] . c[j]   for  0 <= i - j < window,   o[i][h] = sum_j softmax_j(score) c[j]
 // qa [T][H][R] = per-head W_uk^T q; the caller then applies the per-head value up-projection to o [T][H][R].  The latent of
@@ -1048,7 +1167,7 @@ __global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int T
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Layer norm with a weight and no bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w per row of n values.
+// Layer norm with a weight and an optional bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w (+ b) per row of n values.
 // mode 0: out = result; mode 1: out += alpha * result (a normalised sublayer output added into the residual stream).
 // ---------------------------------------------------------------------------------------------------------------------
 // A thread keeps its share of the row in registers (rows of up to 256 * kLnRegs values; longer rows are read again).
@@ -1069,7 +1188,7 @@ __device__ __forceinline__ void ln_stats(const float (&v)[kLnRegs], const float*
   sc = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
 }
 
-__global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, int ld_in, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, int ld_in, const float* __restrict__ w, const float* __restrict__ b,
                                                   float* __restrict__ out, int ld_out, int n, float eps, int mode, float alpha) {
   __shared__ float red[33];
   const int t = blockIdx.x;
@@ -1085,10 +1204,10 @@ __global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, 
 #pragma unroll
     for (int k = 0; k < kLnRegs; k++) {
       const int i = threadIdx.x + 256 * k;
-      if (i < n) { const float r = (v[k] - mean) * sc * w[i]; o[i] = mode == 0 ? r : o[i] + alpha * r; }
+      if (i < n) { const float r = (v[k] - mean) * sc * w[i] + (b ? b[i] : 0.f); o[i] = mode == 0 ? r : o[i] + alpha * r; }
     }
   } else {
-    for (int i = threadIdx.x; i < n; i += 256) { const float r = (x[i] - mean) * sc * w[i]; o[i] = mode == 0 ? r : o[i] + alpha * r; }
+    for (int i = threadIdx.x; i < n; i += 256) { const float r = (x[i] - mean) * sc * w[i] + (b ? b[i] : 0.f); o[i] = mode == 0 ? r : o[i] + alpha * r; }
   }
 }
 
@@ -1130,53 +1249,79 @@ __global__ void add_row(float* __restrict__ x, int ld, const float* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Query / key preparation of grouped-query attention, one CTA per token of the step (position ctl[0] + t):
-//   q <- rot(q / rms(q) * qw),  k <- rot(k / rms(k) * kw)   with the RMS taken over the whole projection (all heads at once);
-//   rot acts on the first rot_dims dimensions of every head: the pair (2i, 2i + 1) turns by the angle pos * freq[i], and cos / sin
-//   are multiplied by `mag`.  Positions and angles are fp32.
+// Query / key preparation of grouped-query attention, one CTA per token of the step (position ctl[0] + t).
+// head_norm == 0:  q <- rot(q / rms(q) * qw),  k <- rot(k / rms(k) * kw)   with the RMS taken over the whole projection (all heads at once);
+// head_norm == 1:  q <- rot(q) / rms_head(rot(q)),  k likewise: every head is divided by its own RMS after the rotation, without a weight.
+//   rot acts on the first rot_dims dimensions of every head: with layout 0 the pair (2i, 2i + 1) turns by the angle pos * freq[i], with
+//   layout 1 the pair (i, i + rot_dims / 2); cos / sin are multiplied by `mag`.  Positions and angles are fp32.
 // q (row pitch ld_q; k: ld_k, v_src: ld_v) goes to q_out; the prepared key goes to row cache_row(pos, keep, ring) of kcache.  Values:
 // with v_src == nullptr the value of a position is the raw output of its key matrix (ahead of the norm and the rotation);
 // otherwise v_src rows are cached, blended with the rows of v_first [T][GV] when that is given: (1 - lam) v + lam v_first.
 // v_keep [T][GV], nullable, receives a copy of what is cached (the rows a later layer blends in).
+// k == nullptr: a layer that reads another layer's caches prepares its queries only and caches nothing.
 // ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float rot_entry(const float* __restrict__ src, int c, int d, int rot_dims, int layout, float nrm, const float* __restrict__ w,
+                                           float fpos, const float* __restrict__ freq, float mag) {
+  float v = src[c] * nrm * (w ? w[c] : 1.f);
+  if (d < rot_dims) {
+    const int half = rot_dims >> 1;
+    const bool second = layout == 1 ? d >= half : (d & 1);      // which entry of its pair this is
+    const int cp = layout == 1 ? (second ? c - half : c + half) : (second ? c - 1 : c + 1);
+    const int pi = layout == 1 ? (second ? d - half : d) : (d >> 1);
+    const float u = src[cp] * nrm * (w ? w[cp] : 1.f);
+    float sn, cs;
+    sincosf(fpos * freq[pi], &sn, &cs);
+    cs *= mag; sn *= mag;
+    v = second ? fmaf(v, cs, u * sn) : fmaf(v, cs, -u * sn);
+  }
+  return v;
+}
 __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q, float* __restrict__ q_out, int HD,
                                                     const float* __restrict__ k, const float* __restrict__ v_src, int GD, int GV, int ld_q, int ld_k, int ld_v,
                                                     const float* __restrict__ qw, const float* __restrict__ kw, float eps, int D,
                                                     int rot_dims, const float* __restrict__ freq, float mag,
                                                     const int* __restrict__ ctl, float* __restrict__ kcache,
                                                     float* __restrict__ vcache, int ring, int keep, const float* __restrict__ v_first,
-                                                    float lam, float* __restrict__ v_keep) {
+                                                    float lam, float* __restrict__ v_keep, int layout, int head_norm) {
   __shared__ float red[33];
   const int t = blockIdx.x, pos = ctl[0] + t;
   const size_t row = (size_t)cache_row(pos, keep, ring);
   const float* qr = q + (size_t)t * ld_q;
-  const float* kr = k + (size_t)t * ld_k;
-  const float* vr = v_src ? v_src + (size_t)t * ld_v : kr;
-  float sq = 0.f, sk = 0.f;
-  for (int e = threadIdx.x; e < HD; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
-  for (int e = threadIdx.x; e < GD; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
-  const float nq = qw ? 1.f / sqrtf(block_sum(sq, red) / (float)HD + eps) : 1.f;
-  const float nk = kw ? 1.f / sqrtf(block_sum(sk, red) / (float)GD + eps) : 1.f;
+  const float* kr = k ? k + (size_t)t * ld_k : nullptr;
   const float fpos = (float)pos;
-  for (int e = threadIdx.x; e < HD + GD; e += blockDim.x) {
-    const bool isq = e < HD;
-    const int c = isq ? e : e - HD, d = c % D;
-    const float* src = isq ? qr : kr;
-    const float* w = isq ? qw : kw;
-    const float nrm = isq ? nq : nk;
-    float v = src[c] * nrm * (w ? w[c] : 1.f);
-    if (d < rot_dims) {
-      const int cp = (d & 1) ? c - 1 : c + 1;                 // the other half of the pair (2i, 2i + 1), counted inside the head
-      const float u = src[cp] * nrm * (w ? w[cp] : 1.f);
-      const float a = fpos * freq[d >> 1];
-      float sn, cs;
-      sincosf(a, &sn, &cs);
-      cs *= mag; sn *= mag;
-      v = (d & 1) ? fmaf(v, cs, u * sn) : fmaf(v, cs, -u * sn);
+  if (!k) GD = 0;
+  if (head_norm) {   // a warp per head: rotated entries are stored, summed, and scaled by the lane that stored them
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nh = (HD + GD) / D;
+    for (int hh = w; hh < nh; hh += 8) {
+      const bool isq = hh * D < HD;
+      const int c0 = isq ? hh * D : hh * D - HD;
+      const float* src = isq ? qr : kr;
+      float* dst = isq ? q_out + (size_t)t * HD + c0 : kcache + row * GD + c0;
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float v = rot_entry(src, c0 + d, d, rot_dims, layout, 1.f, nullptr, fpos, freq, mag);
+        dst[d] = v;
+        ss = fmaf(v, v, ss);
+      }
+      const float sc = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+      for (int d = lane; d < D; d += 32) dst[d] *= sc;
     }
-    if (isq) q_out[(size_t)t * HD + c] = v;
-    else kcache[row * GD + c] = v;
+  } else {
+    float sq = 0.f, sk = 0.f;
+    for (int e = threadIdx.x; e < HD; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
+    for (int e = threadIdx.x; e < GD; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
+    const float nq = qw ? 1.f / sqrtf(block_sum(sq, red) / (float)HD + eps) : 1.f;
+    const float nk = kw && k ? 1.f / sqrtf(block_sum(sk, red) / (float)GD + eps) : 1.f;
+    for (int e = threadIdx.x; e < HD + GD; e += blockDim.x) {
+      const bool isq = e < HD;
+      const int c = isq ? e : e - HD, d = c % D;
+      const float v = rot_entry(isq ? qr : kr, c, d, rot_dims, layout, isq ? nq : nk, isq ? qw : kw, fpos, freq, mag);
+      if (isq) q_out[(size_t)t * HD + c] = v;
+      else kcache[row * GD + c] = v;
+    }
   }
+  if (!k) return;
+  const float* vr = v_src ? v_src + (size_t)t * ld_v : kr;
   for (int e = threadIdx.x; e < GV; e += blockDim.x) {
     float v = vr[e];
     if (v_first) v = fmaf(lam, v_first[(size_t)t * GV + e], (1.f - lam) * v);
@@ -1432,18 +1577,20 @@ __global__ void __launch_bounds__(128) mix_heads(const float* __restrict__ in, f
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Router of a routed feed-forward, one CTA per token.  s = sigmoid(logits); the `top` experts with the largest s + correction
-// are taken (ties: lower index first), slot = rank; weights = s / (sum of the chosen s + 1e-20) * scale.
+// Router of a routed feed-forward, one CTA per token.  mode 0: s = sigmoid(logits); the `top` experts with the largest
+// s + correction are taken (ties: lower index first), slot = rank; weights = s / (sum of the chosen s + 1e-20) * scale.
+// mode 1: the `top` experts with the largest logits are taken (ties: lower index first); weights = softmax over the chosen logits.
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void moe_route(const float* __restrict__ logits, const float* __restrict__ correction, int E, int top, float scale,
-                          int* __restrict__ idx, float* __restrict__ wgt) {
+                          int* __restrict__ idx, float* __restrict__ wgt, int mode) {
   extern __shared__ float sm[];
   float* sc = sm;            // [E]
   float* ch = sm + E;        // [E]
   float* sel = ch + E;       // [top]
   const int t = blockIdx.x;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    const float s = sigmoid_f(logits[(size_t)t * E + e]);
+    const float z = logits[(size_t)t * E + e];
+    const float s = mode == 1 ? z : sigmoid_f(z);
     sc[e] = s;
     ch[e] = s + (correction ? correction[e] : 0.f);
   }
@@ -1456,10 +1603,16 @@ __global__ void moe_route(const float* __restrict__ logits, const float* __restr
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    float sum = 0.f;
-    for (int k = 0; k < top; k++) sum += sel[k];
-    const float inv = scale / (sum + 1e-20f);
-    for (int k = 0; k < top; k++) wgt[(size_t)t * top + k] = sel[k] * inv;
+    if (mode == 1) {   // slot 0 holds the largest logit
+      float sum = 0.f;
+      for (int k = 0; k < top; k++) sum += expf(sel[k] - sel[0]);
+      for (int k = 0; k < top; k++) wgt[(size_t)t * top + k] = expf(sel[k] - sel[0]) / sum;
+    } else {
+      float sum = 0.f;
+      for (int k = 0; k < top; k++) sum += sel[k];
+      const float inv = scale / (sum + 1e-20f);
+      for (int k = 0; k < top; k++) wgt[(size_t)t * top + k] = sel[k] * inv;
+    }
   }
 }
 

@@ -12,6 +12,9 @@
 //   mlp.router, mlp.correction, mlp.e<j>.gate|up|down                                                 (routed feed-forward)
 //   mlp.up, mlp.up.b, mlp.down, mlp.down.b, mlp.act                                                   (dense feed-forward)
 //   side.gate, side.proj, side.norm                                                                   (per-layer token input)
+//   shift (token shift), norm1.b / norm2.b / final.norm.b (layer norms with a bias)
+//         | mix.q, mix.f, mix.f.b, mix.lower, mix.v, mix.norm, mix.o                                   (gated linear recurrence)
+//   mlp.router, mlp.router.b, mlp.e<j>.up|down                                                        (routed feed-forward, top-softmax router)
 // Grouped-query attention with its switches on adds mix.v, mix.q.b / k.b / v.b, mix.rel, mix.sink, mix.vmix; latent attention with a
 // rotated key part (DSK_MIX_MLA) has mix.dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o; a gated dense feed-forward mlp.gate / up / down;
 // DSK_BLOCK_POST layers norm1 / norm2, ls1 / ls2, canon1 / canon2, rg1 / rg2 (+ .b); the model "bigram" beside "embed".
@@ -74,6 +77,13 @@ struct HLayer {
   // per-layer token input
   HTensor sgate, sproj;
   float* snorm = nullptr;
+  // token shift weight; biases of the layer norms; bias of a top-softmax router
+  float *shift = nullptr, *norm1_bias = nullptr, *norm2_bias = nullptr, *router_b = nullptr;
+  // gated linear recurrence: [q | f | v] rows stacked into one matrix, the forget gate's bias at the f rows of a stacked bias
+  // (zeros elsewhere), lower bounds, and the output norm's weight repeated for every head
+  HTensor lin_in;
+  float *lin_bias = nullptr, *lower = nullptr, *lin_norm = nullptr;
+  char have_lin[3] = {0, 0, 0}, have_linb = 0;
 };
 
 // one execution of a layer: layers inside the loop range run once per pass, each time with a state of their own
@@ -88,7 +98,7 @@ struct Model {
   std::vector<HLayer> L;
   std::vector<Run> runs;
   HTensor embed, side_embed, head, bigram;
-  float *final_norm = nullptr, *loop_step = nullptr;
+  float *final_norm = nullptr, *final_norm_b = nullptr, *loop_step = nullptr;
   int vmix_first = -1;              // the first layer whose values later value-mixing layers blend in
   size_t wsize = 4;                 // bytes per matrix element
 };
@@ -99,7 +109,9 @@ struct LayerState {
   void* cache = nullptr;            // [ring][kv_rank] (owner layers); grouped-query attention: keys [ring][kv_heads * dim]
   void* vcache = nullptr;           // grouped-query attention: values [ring][kv_heads * vdim]
   float* canon = nullptr;           // DSK_BLOCK_POST: [2][taps - 1][width] rings of the two input convolutions
-  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0, vcache_bytes = 0, canon_bytes = 0;
+  float* shift = nullptr;           // token shift: the mixer input of the sequence's last token [width]
+  float* lin = nullptr;             // gated linear recurrence: [heads][dim][vdim]
+  size_t ssm_bytes = 0, hist_bytes = 0, cache_bytes = 0, vcache_bytes = 0, canon_bytes = 0, shift_bytes = 0, lin_bytes = 0;
 };
 
 struct State {
@@ -117,6 +129,7 @@ struct State {
   int* d_rows = nullptr;
   int prefill_keys = 0;                      // keys a block of queries can see at most; 0: the matrix path is off
   float* y = nullptr;                        // a sublayer's output before its closing norm (sandwich and post blocks)
+  float* hs = nullptr;                       // the token-shifted mixer input of the step
   float* vfirst = nullptr;                   // [chunk][kv_heads * vdim] values of the step's tokens in the first value-mixing layer
   int* d_prev = nullptr;                     // the sequence's last token (bigram embedding)
   float *x = nullptr, *h = nullptr, *b0 = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *wgt = nullptr, *logits = nullptr;
@@ -146,8 +159,11 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
   if (c.chunk < 1 || c.chunk > 4096) return fail(-1, "chunk %d out of range (1..4096)", c.chunk);
   if (c.side_dim < 0) return fail(-1, "negative side_dim");
   if (c.block != DSK_BLOCK_PARALLEL && c.block != DSK_BLOCK_SANDWICH && c.block != DSK_BLOCK_POST) return fail(-1, "unknown block kind %d", c.block);
-  if (c.block == DSK_BLOCK_POST && (c.norm_kind != DSK_NORM_RMS || c.norm_groups != 1 || c.side_dim > 0 || c.loop_times >= 1))
-    return fail(-1, "post-norm blocks run with plain RMS norms, without a per-layer token input and without a layer loop");
+  if (c.block == DSK_BLOCK_POST && (c.norm_groups != 1 || c.loop_times >= 1))
+    return fail(-1, "post-norm blocks run with ungrouped norms and without a layer loop");
+  if (c.block == DSK_BLOCK_POST && c.norm_kind == DSK_NORM_LAYER && c.norm_scalar) return fail(-1, "single-number norm weights belong to RMS norms");
+  if (c.norm_bias && c.norm_kind != DSK_NORM_LAYER) return fail(-1, "norm biases belong to layer norms");
+  if (c.norm_bias && c.block == DSK_BLOCK_SANDWICH) return fail(-1, "sandwich blocks run their layer norms without a bias");
   if (c.block != DSK_BLOCK_POST && (c.canon_taps || c.res_gate || c.layer_scale || c.norm_scalar))
     return fail(-1, "input convolutions, gated residuals, layer scales and single-number norm weights belong to post-norm blocks");
   if (c.canon_taps < 0 || c.canon_taps > kCanonMaxTaps) return fail(-1, "input convolution of %d taps unsupported (at most %d)", c.canon_taps, kCanonMaxTaps);
@@ -182,6 +198,20 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
       if (s.att_rel_max < 0 || s.att_softcap < 0.f) return fail(-1, "layer %d: negative score cap or distance limit", i);
       if (s.rot_dims < 0 || s.rot_dims > s.att_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most dim %d", i, s.rot_dims, s.att_dim);
       if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
+      if ((s.rot_layout != DSK_ROT_PAIRS && s.rot_layout != DSK_ROT_HALF) || (s.rot_scale != DSK_ROTSCALE_YARN && s.rot_scale != DSK_ROTSCALE_BANDS) ||
+          (s.att_qk_norm != DSK_QKNORM_WHOLE && s.att_qk_norm != DSK_QKNORM_HEAD))
+        return fail(-1, "layer %d: unknown rotation layout, rotation scaling or query / key norm", i);
+      if (s.rot_scale == DSK_ROTSCALE_BANDS && s.rot_factor > 0.f && (!(s.rot_fast > s.rot_slow) || s.rot_original <= 0))
+        return fail(-1, "layer %d: wavelength-band rotation scaling needs high > low and a positive original length", i);
+      if (s.att_kv_from >= 0) {
+        const int j = s.att_kv_from;
+        if (j >= i || L[j].mixer != DSK_MIX_GQA || L[j].att_kv_from >= 0)
+          return fail(-1, "layer %d: kv_from %d must name an earlier attention layer that projects its own keys and values", i, j);
+        const dsk_layer_spec& o = L[j];
+        if (o.att_kv_heads != s.att_kv_heads || o.att_dim != s.att_dim || o.att_vdim != s.att_vdim || o.att_keep_first != s.att_keep_first || !o.att_value_proj ||
+            !s.att_value_proj || s.att_vmix || s.att_bias)
+          return fail(-1, "layer %d: a layer that reads layer %d's keys and values needs its key heads, sizes and kept positions, a value matrix there, and no biases or value mixing of its own", i, j);
+      }
       if (gqa_attn_smem_floats(s.att_heads, s.att_kv_heads, s.att_dim, s.att_vdim) * 4 > 200 * 1024)
         return fail(-1, "layer %d: %d heads x %d with %d key heads do not fit the attention kernel's shared memory", i, s.att_heads, s.att_dim, s.att_kv_heads);
     } else if (s.mixer == DSK_MIX_MLA) {
@@ -190,14 +220,19 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
       if (s.att_kv_rank + s.att_rot_dim > 1024) return fail(-1, "layer %d: kv_rank + rot_dim %d > 1024 unsupported", i, s.att_kv_rank + s.att_rot_dim);
       if (s.rot_dims < 0 || s.rot_dims > s.att_rot_dim || s.rot_dims % 2 != 0) return fail(-1, "layer %d: rot dims %d must be even and at most rot_dim %d", i, s.rot_dims, s.att_rot_dim);
       if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail(-1, "layer %d: bad rotation base", i);
+    } else if (s.mixer == DSK_MIX_HGRN2) {
+      if (s.lin_heads <= 0 || s.lin_dim <= 0 || s.lin_vdim <= 0) return fail(-1, "layer %d: bad linear-recurrence sizes", i);
+      if (s.lin_dim > 256) return fail(-1, "layer %d: key size %d > 256 unsupported (the recurrence keeps the state in registers)", i, s.lin_dim);
     } else return fail(-1, "layer %d: unknown mixer %d", i, s.mixer);
-    if (s.mixer != DSK_MIX_SSD && s.att_mask != DSK_MASK_WINDOW && s.att_mask != DSK_MASK_CHUNK) return fail(-1, "layer %d: unknown mask %d", i, s.att_mask);
+    if (s.mixer != DSK_MIX_SSD && s.mixer != DSK_MIX_HGRN2 && s.att_mask != DSK_MASK_WINDOW && s.att_mask != DSK_MASK_CHUNK) return fail(-1, "layer %d: unknown mask %d", i, s.att_mask);
     if (s.ff_kind == DSK_FF_DENSE) {
       if (s.ff_hidden <= 0) return fail(-1, "layer %d: bad feed-forward size", i);
       if (s.ff_act != DSK_ACT_XIELU && s.ff_act != DSK_ACT_GEGLU) return fail(-1, "layer %d: unknown activation %d", i, s.ff_act);
     } else if (s.ff_kind == DSK_FF_MOE) {
       if (s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || s.ff_hidden <= 0) return fail(-1, "layer %d: bad routed feed-forward sizes", i);
       if (s.ff_experts > 4096) return fail(-1, "layer %d: more than 4096 experts unsupported", i);
+      if ((s.ff_router != DSK_ROUTER_SIGMOID && s.ff_router != DSK_ROUTER_TOP_SOFTMAX) || (s.ff_expert != DSK_EXPERT_GLU_CLAMPED && s.ff_expert != DSK_EXPERT_RELU2))
+        return fail(-1, "layer %d: unknown router or expert kind", i);
     } else if (s.ff_kind != DSK_FF_NONE) return fail(-1, "layer %d: unknown feed-forward kind %d", i, s.ff_kind);
   }
   return 0;
@@ -221,6 +256,10 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_mma<HEPI_XIELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_SIGMUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(hgrn2_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(gqa_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(mix_heads, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
@@ -246,7 +285,8 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
     L.sp = layers[i];
     if (L.sp.ff_kind == DSK_FF_MOE) L.have.assign(3 * (size_t)L.sp.ff_experts, 0);
     if (L.sp.mixer == DSK_MIX_LATENT_SWA) L.owner = L.sp.att_kv_from >= 0 ? L.sp.att_kv_from : i;
-    if (L.sp.mixer == DSK_MIX_GQA || L.sp.mixer == DSK_MIX_MLA) L.owner = i;
+    if (L.sp.mixer == DSK_MIX_GQA) L.owner = L.sp.att_kv_from >= 0 ? L.sp.att_kv_from : i;
+    if (L.sp.mixer == DSK_MIX_MLA) L.owner = i;
     if (L.sp.mixer == DSK_MIX_GQA && L.sp.att_vmix) {
       if (M->vmix_first < 0) M->vmix_first = i;
       else if ((long long)L.sp.att_kv_heads * L.sp.att_vdim != (long long)M->L[M->vmix_first].sp.att_kv_heads * M->L[M->vmix_first].sp.att_vdim) {
@@ -284,7 +324,8 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
     const int half = s.rot_dims / 2;
     std::vector<float> f((size_t)half);
     const double base = s.rot_base, dims = s.rot_dims;
-    const bool yarn = s.rot_factor > 0.f;
+    const bool yarn = s.rot_factor > 0.f && (s.mixer != DSK_MIX_GQA || s.rot_scale == DSK_ROTSCALE_YARN);
+    const bool bands = s.rot_factor > 0.f && s.mixer == DSK_MIX_GQA && s.rot_scale == DSK_ROTSCALE_BANDS;
     double lo = 0, hi = 0;
     if (yarn) {   // the pair index at which `original` positions hold t turns
       auto at = [&](double t) { return dims * std::log((double)s.rot_original / (2.0 * M_PI * t)) / (2.0 * std::log(base)); };
@@ -297,6 +338,14 @@ static dsk_model* model_create(const dsk_hybrid_config* cfg, const dsk_layer_spe
       if (yarn) {
         const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
         fr = fr / s.rot_factor * ramp + fr * (1.0 - ramp);
+      }
+      if (bands) {   // by wavelength: short ones keep their frequency, long ones are slowed by the factor, a linear blend between
+        const double wl = 2.0 * M_PI / fr, orig = s.rot_original;
+        if (wl > orig / s.rot_slow) fr = fr / s.rot_factor;
+        else if (!(wl < orig / s.rot_fast)) {
+          const double sm = (orig / wl - s.rot_slow) / ((double)s.rot_fast - s.rot_slow);
+          fr = (1.0 - sm) * fr / s.rot_factor + sm * fr;
+        }
       }
       f[k] = (float)fr;
     }
@@ -401,6 +450,7 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
     return 0;
   }
   if (nm == "final.norm") return F32(&M->final_norm, c.dim, 0);
+  if (nm == "final.norm.b" && c.norm_bias) return F32(&M->final_norm_b, c.dim, 0);
   if (nm == "head") {
     if (c.tie_head) return fail(-4, "tensor %s: this model's LM head is its embedding table", name);
     return MAT(M->head, c.vocab_size, c.dim);
@@ -420,6 +470,11 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
   HLayer& L = M->L[li];
   const dsk_layer_spec& s = L.sp;
   const std::string rest(end + 1);
+  if (rest == "shift" && c.token_shift) return F32(&L.shift, c.dim, 0);
+  if (c.norm_bias) {
+    if (rest == "norm1.b") return F32(&L.norm1_bias, c.dim, 0);
+    if (rest == "norm2.b" && s.ff_kind != DSK_FF_NONE) return F32(&L.norm2_bias, c.dim, 0);
+  }
   if (c.block == DSK_BLOCK_POST) {
     const bool ff = s.ff_kind != DSK_FF_NONE;
     if (rest == "norm1") return c.norm_scalar ? SCALAR(&L.norm1_s, &L.have_n1) : F32(&L.norm1, c.dim, 0);
@@ -456,6 +511,24 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "D") return F32(&L.D, s.ssm_heads, 0);
       if (k == "norm") return F32(&L.mnorm, inner, 0);
       if (k == "o") return MAT(L.o, c.dim, inner);
+    } else if (s.mixer == DSK_MIX_HGRN2) {
+      const long long HN = (long long)s.lin_heads * s.lin_dim, HP = (long long)s.lin_heads * s.lin_vdim, tot = 2 * HN + HP;
+      if (k == "q") return STACK(L.lin_in, tot, c.dim, 0, HN, &L.have_lin[0]);
+      if (k == "f") return STACK(L.lin_in, tot, c.dim, HN, HN, &L.have_lin[1]);
+      if (k == "v") return STACK(L.lin_in, tot, c.dim, 2 * HN, HP, &L.have_lin[2]);
+      if (k == "f.b") {   // the bias of the stacked product: zeros at the q and v rows
+        if (!L.lin_bias) { if (dmalloc(m, (void**)&L.lin_bias, (size_t)tot * 4)) return -2; CK(cudaMemset(L.lin_bias, 0, (size_t)tot * 4)); }
+        return STACKV(&L.lin_bias, tot, HN, HN, &L.have_linb);
+      }
+      if (k == "lower") return F32(&L.lower, HN, 0);
+      if (k == "o") return MAT(L.o, c.dim, HP);
+      if (k == "norm") {   // one weight vector for all heads: kept repeated per head, so the grouped RMS norm kernel serves
+        if (L.lin_norm) return fail(-4, "tensor %s uploaded twice", name);
+        if (dmalloc(m, (void**)&L.lin_norm, (size_t)HP * 4)) return -2;
+        for (int h = 0; h < s.lin_heads; h++)
+          if (int rc = put(name, dtype, shape, data, nbytes, on_dev, s.lin_vdim, 0, L.lin_norm + (size_t)h * s.lin_vdim, false, 0)) return rc;
+        return 0;
+      }
     } else if (s.mixer == DSK_MIX_MLA) {
       const long long H = s.att_heads, DK = s.att_dim + s.att_rot_dim, R = s.att_kv_rank, Q = s.att_q_rank, tot = Q + R + s.att_rot_dim;
       if (k == "dq") return STACK(L.in2, tot, c.dim, 0, Q, &L.have_in2[0]);
@@ -469,7 +542,10 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "o") return MAT(L.o, c.dim, H * s.att_vdim);
     } else if (s.mixer == DSK_MIX_GQA) {
       const long long HD = (long long)s.att_heads * s.att_dim, GD = (long long)s.att_kv_heads * s.att_dim, GV = (long long)s.att_kv_heads * s.att_vdim;
-      if (s.att_value_proj) {
+      if (k == "g" && s.att_out_gate) return MAT(L.gmat, (long long)s.att_heads * s.att_vdim, c.dim);
+      if (s.att_kv_from >= 0) {   // reads another layer's keys and values: only the query projection of its own
+        if (k == "q") return MAT(L.q, HD, c.dim);
+      } else if (s.att_value_proj) {
         const long long tot = HD + GD + GV;
         if (k == "q") return STACK(L.qkv, tot, c.dim, 0, HD, &L.have_qkv[0]);
         if (k == "k") return STACK(L.qkv, tot, c.dim, HD, GD, &L.have_qkv[1]);
@@ -490,8 +566,8 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "vmix" || (k == "rel" && s.att_rel_max <= 0)) return 0;   // a checkpoint may carry them for layers that do not use them
       if (k == "q" && !s.att_value_proj) return MAT(L.q, HD, c.dim);
       if (k == "k" && !s.att_value_proj) return MAT(L.kproj, GD, c.dim);
-      if (k == "q.norm") return F32(&L.q_norm, HD, 0);
-      if (k == "k.norm") return F32(&L.k_norm, GD, 0);
+      if (k == "q.norm" && s.att_qk_norm == DSK_QKNORM_WHOLE) return F32(&L.q_norm, HD, 0);
+      if (k == "k.norm" && s.att_qk_norm == DSK_QKNORM_WHOLE) return F32(&L.k_norm, GD, 0);
       if (k == "talk" && s.att_talk) return F32(&L.talk, s.att_heads, s.att_heads);
       if (k == "o") return MAT(L.o, c.dim, (long long)s.att_heads * s.att_vdim);
     } else {
@@ -535,14 +611,15 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
     const std::string k = rest.substr(4);
     const long long E = s.ff_experts, ff = s.ff_hidden;
     if (k == "router") return F32(&L.router, E, c.dim);
-    if (k == "correction") return F32(&L.correction, E, 0);
+    if (k == "correction" && s.ff_router == DSK_ROUTER_SIGMOID) return F32(&L.correction, E, 0);
+    if (k == "router.b" && s.ff_router == DSK_ROUTER_TOP_SOFTMAX) return F32(&L.router_b, E, 0);
     if (k.size() > 1 && k[0] == 'e') {
       char* e2 = nullptr;
       const long e = strtol(k.c_str() + 1, &e2, 10);
       if (e2 != k.c_str() + 1 && *e2 == '.' && e >= 0 && e < E) {
         const std::string part(e2 + 1);
         const int which = part == "gate" ? 0 : part == "up" ? 1 : part == "down" ? 2 : -1;
-        if (which >= 0) {
+        if (which >= (s.ff_expert == DSK_EXPERT_RELU2 ? 1 : 0)) {
           HTensor& st = which == 0 ? L.gate_s : which == 1 ? L.up_s : L.down_s;
           if (!st.p) {
             if (dmalloc(m, &st.p, (size_t)E * ff * c.dim * M->wsize + 16)) return -2;
@@ -570,6 +647,7 @@ static int finalize(dsk_model* m) {
   const dsk_hybrid_config& c = M->c;
   if (!M->embed.present) return fail(-5, "missing tensor embed");
   if (!M->final_norm) return fail(-5, "missing tensor final.norm");
+  if (c.norm_bias && !M->final_norm_b) return fail(-5, "missing tensor final.norm.b");
   if (c.side_dim > 0 && !M->side_embed.present) return fail(-5, "missing tensor side.embed");
   if (!c.tie_head && !M->head.present) return fail(-5, "missing tensor head");
   if (c.bigram_buckets > 0 && !M->bigram.present) return fail(-5, "missing tensor bigram");
@@ -596,14 +674,23 @@ static int finalize(dsk_model* m) {
       if (c.res_gate && (!L.rg1.present || !L.rg1_b || (ff && (!L.rg2.present || !L.rg2_b)))) return fail(-5, "layer %d: missing residual gate tensors (rg1, rg1.b, rg2, rg2.b)", i);
       if (fold(L.norm1, L.norm1_s, L.ls1, &L.close1) || (ff && fold(L.norm2, L.norm2_s, L.ls2, &L.close2))) return -2;
     } else if (!L.norm1) return fail(-5, "missing tensor l%d.norm1", i);
+    if (c.token_shift && !L.shift) return fail(-5, "missing tensor l%d.shift", i);
+    if (c.norm_bias && (!L.norm1_bias || (s.ff_kind != DSK_FF_NONE && !L.norm2_bias))) return fail(-5, "layer %d: missing norm biases (norm1.b, norm2.b)", i);
     if (c.block == DSK_BLOCK_SANDWICH && (!L.norm1b || (s.ff_kind != DSK_FF_NONE && (!L.norm2 || !L.norm2b))))
       return fail(-5, "layer %d: missing norm tensors (norm1b, norm2, norm2b)", i);
-    if (s.mixer == DSK_MIX_GQA) {
-      if (s.att_value_proj) {
+    if (s.mixer == DSK_MIX_HGRN2) {
+      L.lin_in.present = L.have_lin[0] && L.have_lin[1] && L.have_lin[2];
+      if (!L.lin_in.present || !L.have_linb || !L.lower || !L.lin_norm || !L.o.present)
+        return fail(-5, "layer %d: missing linear-recurrence tensors (mix.q, f, f.b, lower, v, norm, o)", i);
+    } else if (s.mixer == DSK_MIX_GQA) {
+      if (s.att_out_gate && !L.gmat.present) return fail(-5, "layer %d: missing tensor mix.g", i);
+      if (s.att_kv_from >= 0) {
+        if (!L.q.present) return fail(-5, "layer %d: missing tensor mix.q", i);
+      } else if (s.att_value_proj) {
         L.qkv.present = L.have_qkv[0] && L.have_qkv[1] && L.have_qkv[2];
         if (!L.qkv.present || (s.att_bias && !(L.have_qkvb[0] && L.have_qkvb[1] && L.have_qkvb[2]))) return fail(-5, "layer %d: missing attention projections (mix.q, k, v and their biases)", i);
       } else if (!L.q.present || !L.kproj.present) return fail(-5, "layer %d: missing attention tensors (mix.q, k)", i);
-      if (!L.o.present || !L.q_norm || !L.k_norm || (s.att_talk && !L.talk))
+      if (!L.o.present || (s.att_qk_norm == DSK_QKNORM_WHOLE && (!L.q_norm || !L.k_norm)) || (s.att_talk && !L.talk))
         return fail(-5, "layer %d: missing attention tensors (mix.q.norm, k.norm, talk, o)", i);
       if ((s.att_sink && !L.sink) || (s.att_rel_max > 0 && !L.rel) || (s.att_vmix && !L.have_vmix && i != M->vmix_first))
         return fail(-5, "layer %d: missing attention tensors (mix.sink, rel, vmix)", i);
@@ -632,8 +719,8 @@ static int finalize(dsk_model* m) {
     } else if (s.ff_kind == DSK_FF_DENSE && (!L.up.present || !L.down.present || !L.up_b || !L.down_b || !L.act))
       return fail(-5, "layer %d: missing feed-forward tensors (mlp.up, up.b, down, down.b, act)", i);
     if (s.ff_kind == DSK_FF_MOE) {
-      if (!L.router || !L.correction) return fail(-5, "layer %d: missing mlp.router / mlp.correction", i);
-      for (size_t k = 0; k < L.have.size(); k++)
+      if (!L.router || (s.ff_router == DSK_ROUTER_SIGMOID ? !L.correction : !L.router_b)) return fail(-5, "layer %d: missing mlp.router / mlp.correction / mlp.router.b", i);
+      for (size_t k = s.ff_expert == DSK_EXPERT_RELU2 ? (size_t)s.ff_experts : 0; k < L.have.size(); k++)
         if (!L.have[k]) return fail(-5, "layer %d: missing expert tensor mlp.e%zu.%s", i, k % s.ff_experts, k / s.ff_experts == 0 ? "gate" : k / s.ff_experts == 1 ? "up" : "down");
     }
     if (c.side_dim > 0 && (!L.sgate.present || !L.sproj.present || !L.snorm)) return fail(-5, "layer %d: missing side.gate / side.proj / side.norm", i);
@@ -659,10 +746,17 @@ static double active_bytes(const dsk_model* m) {
       f32 += subs * (W * c.canon_taps + (c.res_gate ? W : 0)) + (subs - 1) * W;
       if (c.res_gate) mat += subs * W * W;
     }
-    if (s.mixer == DSK_MIX_GQA) {
-      const double HD = (double)s.att_heads * s.att_dim, GD = (double)s.att_kv_heads * s.att_dim, GV = s.att_value_proj ? (double)s.att_kv_heads * s.att_vdim : 0.0;
-      mat += (HD + GD + GV) * W + W * s.att_heads * s.att_vdim;
-      f32 += HD + GD + (s.att_talk ? (double)s.att_heads * s.att_heads : 0.0) + (s.att_bias ? HD + GD + GV : 0.0) + (s.att_sink ? s.att_heads : 0);
+    if (c.token_shift) f32 += W;
+    if (c.norm_bias) f32 += W * (s.ff_kind != DSK_FF_NONE ? 2 : 1);
+    if (s.mixer == DSK_MIX_HGRN2) {
+      const double HN = (double)s.lin_heads * s.lin_dim, HP = (double)s.lin_heads * s.lin_vdim;
+      mat += (2 * HN + HP) * W + W * HP;
+      f32 += 3 * HN + 2 * HP;
+    } else if (s.mixer == DSK_MIX_GQA) {
+      const bool reads = s.att_kv_from >= 0;
+      const double HD = (double)s.att_heads * s.att_dim, GD = reads ? 0.0 : (double)s.att_kv_heads * s.att_dim, GV = s.att_value_proj && !reads ? (double)s.att_kv_heads * s.att_vdim : 0.0;
+      mat += (HD + GD + GV) * W + W * s.att_heads * s.att_vdim * (s.att_out_gate ? 2 : 1);
+      f32 += (s.att_qk_norm == DSK_QKNORM_WHOLE ? HD + GD : 0.0) + (s.att_talk ? (double)s.att_heads * s.att_heads : 0.0) + (s.att_bias ? HD + GD + GV : 0.0) + (s.att_sink ? s.att_heads : 0);
     } else if (s.mixer == DSK_MIX_MLA) {
       const double H = s.att_heads, DK = s.att_dim + s.att_rot_dim, Rr = s.att_kv_rank, Q = s.att_q_rank;
       mat += (Q + Rr + s.att_rot_dim) * W + H * DK * Q + H * (s.att_dim + s.att_vdim) * Rr + (s.att_out_gate ? H * s.att_vdim * W : 0.0) + W * H * s.att_vdim;
@@ -672,7 +766,7 @@ static double active_bytes(const dsk_model* m) {
       mat += (double)s.att_heads * s.att_dim * W + (double)s.att_heads * (s.att_dim + s.att_vdim) * s.att_kv_rank + W * s.att_heads * s.att_vdim;
       if (s.att_kv_from < 0) { mat += (double)s.att_kv_rank * W; f32 += s.att_kv_rank; }
     }
-    if (s.ff_kind == DSK_FF_MOE) { mat += 3.0 * s.ff_top * s.ff_hidden * W; f32 += (double)s.ff_experts * (W + 1); }
+    if (s.ff_kind == DSK_FF_MOE) { mat += (s.ff_expert == DSK_EXPERT_RELU2 ? 2.0 : 3.0) * s.ff_top * s.ff_hidden * W; f32 += (double)s.ff_experts * (W + 1); }
     if (s.ff_kind == DSK_FF_DENSE && s.ff_act == DSK_ACT_GEGLU) mat += 3.0 * s.ff_hidden * W;
     else if (s.ff_kind == DSK_FF_DENSE) { mat += 2.0 * s.ff_hidden * W; f32 += s.ff_hidden + W; }
     if (c.side_dim > 0) { mat += 2.0 * c.side_dim * W + c.side_dim; f32 += W; }
@@ -691,12 +785,15 @@ static int launches_per_token(const dsk_model* m) {
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0)) + (&R == &M->runs[0] && M->c.canon_taps > 0 ? 1 : 0);   // gate, closing norm + next convolution in one
+    if (M->c.token_shift) n += 1;
+    if (post && M->c.canon_taps <= 0) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0));   // gate, closing norm
+    else if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0)) + (&R == &M->runs[0] && M->c.canon_taps > 0 ? 1 : 0);   // gate, closing norm + next convolution in one
     else if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
     else n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
-    if (s.mixer == DSK_MIX_GQA) n += s.att_value_proj ? 5 : 6;   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, o
+    if (s.mixer == DSK_MIX_HGRN2) n += 4;   // stacked projection, recurrence, head norm, o
+    else if (s.mixer == DSK_MIX_GQA) n += (s.att_value_proj ? 5 : 6) + (s.att_out_gate ? 1 : 0);   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, (gate,) o
     else if (s.mixer == DSK_MIX_MLA) n += 10 + (s.att_out_gate ? 1 : 0);   // down-projections, query norm, query up, latent preparation, absorbed query, attention, merge, value up, (gate,) o
-    else if (s.mixer != DSK_MIX_MLA) n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
+    else if (s.mixer != DSK_MIX_MLA && s.mixer != DSK_MIX_HGRN2 && s.mixer != DSK_MIX_GQA) n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
     if (s.ff_kind == DSK_FF_MOE) n += 5;
     if (s.ff_kind == DSK_FF_DENSE) n += 2;
     if (M->c.side_dim > 0) n += 3;
@@ -722,6 +819,8 @@ static int state_reset(dsk_state* s) {
     if (l.cache) CK(cudaMemsetAsync(l.cache, 0, l.cache_bytes, s->stream));
     if (l.vcache) CK(cudaMemsetAsync(l.vcache, 0, l.vcache_bytes, s->stream));
     if (l.canon) CK(cudaMemsetAsync(l.canon, 0, l.canon_bytes, s->stream));
+    if (l.shift) CK(cudaMemsetAsync(l.shift, 0, l.shift_bytes, s->stream));
+    if (l.lin) CK(cudaMemsetAsync(l.lin, 0, l.lin_bytes, s->stream));
   }
   S->next_pos = 0;
   s->last_pos = -1;
@@ -764,12 +863,23 @@ static dsk_state* state_create(dsk_model* m) {
       ls.canon_bytes = (size_t)2 * (c.canon_taps - 1) * c.dim * 4;
       if (salloc(S, (void**)&ls.canon, ls.canon_bytes)) return nullptr;
     }
-    if (sp.mixer == DSK_MIX_GQA) {
+    if (c.token_shift) {
+      ls.shift_bytes = (size_t)c.dim * 4;
+      if (salloc(S, (void**)&ls.shift, ls.shift_bytes)) return nullptr;
+    }
+    if (sp.mixer == DSK_MIX_HGRN2) {
+      const size_t HN = (size_t)sp.lin_heads * sp.lin_dim, HP = (size_t)sp.lin_heads * sp.lin_vdim;
+      ls.lin_bytes = HN * sp.lin_vdim * 4;
+      if (salloc(S, (void**)&ls.lin, ls.lin_bytes)) return nullptr;
+      mx0 = std::max<size_t>(mx0, 2 * HN + HP); mx2 = std::max<size_t>(mx2, HP); mx3 = std::max<size_t>(mx3, HP);
+    } else if (sp.mixer == DSK_MIX_GQA) {
       const size_t HD = (size_t)sp.att_heads * sp.att_dim, GD = (size_t)sp.att_kv_heads * sp.att_dim, GV = (size_t)sp.att_kv_heads * sp.att_vdim;
-      const size_t rows = (size_t)sp.att_keep_first + L.ring;   // the kept first positions have rows of their own in front of the ring
-      ls.cache_bytes = rows * GD * 4;
-      ls.vcache_bytes = rows * GV * 4;
-      if (salloc(S, &ls.cache, ls.cache_bytes) || salloc(S, &ls.vcache, ls.vcache_bytes)) return nullptr;
+      if (M->runs[r].owner_run == (int)r) {   // a layer that reads another layer's keys and values caches nothing
+        const size_t rows = (size_t)sp.att_keep_first + L.ring;   // the kept first positions have rows of their own in front of the ring
+        ls.cache_bytes = rows * GD * 4;
+        ls.vcache_bytes = rows * GV * 4;
+        if (salloc(S, &ls.cache, ls.cache_bytes) || salloc(S, &ls.vcache, ls.vcache_bytes)) return nullptr;
+      }
       mx0 = std::max<size_t>(mx0, sp.att_value_proj ? HD + GD + GV : HD); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
       mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_vdim);
       any_talk |= sp.att_talk != 0;
@@ -822,7 +932,7 @@ static dsk_state* state_create(dsk_model* m) {
     size_t keys = 0, hd = 0, hv = 0, heads = 0, pack_es = 0;
     bool latent = false;
     for (const HLayer& L : M->L) {
-      if (L.sp.mixer == DSK_MIX_SSD) continue;
+      if (L.sp.mixer == DSK_MIX_SSD || L.sp.mixer == DSK_MIX_HGRN2) continue;
       const size_t kh = L.sp.mixer == DSK_MIX_GQA ? L.sp.att_kv_heads : L.sp.att_heads;
       latent |= L.sp.mixer == DSK_MIX_LATENT_SWA || L.sp.mixer == DSK_MIX_MLA;
       if (L.sp.mixer == DSK_MIX_LATENT_SWA) pack_es = std::max(pack_es, M->wsize);
@@ -843,6 +953,7 @@ static dsk_state* state_create(dsk_model* m) {
   }
   rc |= salloc(S, (void**)&S->x, Tc * c.dim * 4) | salloc(S, (void**)&S->h, Tc * c.dim * 4);
   if (c.block != DSK_BLOCK_PARALLEL) rc |= salloc(S, (void**)&S->y, Tc * c.dim * 4);
+  if (c.token_shift) rc |= salloc(S, (void**)&S->hs, Tc * c.dim * 4);
   if (mxGV) rc |= salloc(S, (void**)&S->vfirst, Tc * mxGV * 4);
   rc |= salloc(S, (void**)&S->d_prev, 16);
   rc |= salloc(S, (void**)&S->b0, Tc * mx0 * 4) | salloc(S, (void**)&S->b1, Tc * mx1 * 4) | salloc(S, (void**)&S->b2, Tc * mx2 * 4) | salloc(S, (void**)&S->b3, Tc * mx3 * 4);
@@ -911,6 +1022,7 @@ static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaSt
     case HEPI_XIELU: gemm_mma<HEPI_XIELU><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_GEGLU: gemm_mma<HEPI_GEGLU><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_SIGMUL: gemm_mma<HEPI_SIGMUL><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_RELU2: gemm_mma<HEPI_RELU2><<<grid, 256, kMmaSmem, st>>>(P); break;
     default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, kMmaSmem, st>>>(P); break;
   }
 }
@@ -926,6 +1038,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_XIELU: gemv_rows<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GEGLU: gemv_rows<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_SIGMUL: gemv_rows<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_RELU2: gemv_rows<WT, HEPI_RELU2><<<grid, 256, 0, st>>>(P); break;
       default: gemv_rows<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   } else {
@@ -937,6 +1050,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_XIELU: gemm_tiled<WT, HEPI_XIELU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_GEGLU: gemm_tiled<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_SIGMUL: gemm_tiled<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_RELU2: gemm_tiled<WT, HEPI_RELU2><<<grid, 256, 0, st>>>(P); break;
       default: gemm_tiled<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   }
@@ -979,6 +1093,22 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
 #undef DSK_SCAN
 }
 
+static void launch_hgrn2(const dsk_layer_spec& sp, const float* proj, int ld, const float* lower, float* state, float* out, int T, cudaStream_t st) {
+  const int H = sp.lin_heads, N = sp.lin_dim, P = sp.lin_vdim;
+  int PB = std::min(P, 64);   // value channels per CTA: fewer when the heads alone would leave most SMs idle
+  while (PB > 8 && H * ((P + PB - 1) / PB) < 148) PB /= 2;
+  const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
+  const int threads = ((PB * 8 + 31) / 32) * 32;
+  const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
+  const int NP = (N + 3) & ~3;
+  const size_t smem = (size_t)TB * (2 * NP + PB) * 4;
+  const int need = (N + 31) / 32;     // float4 groups of state per thread
+#define DSK_LIN(RQ) hgrn2_scan<RQ><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, lower, state, out, H * P, T, H, N, P, PB, TB)
+  if (need <= 1) DSK_LIN(1); else if (need <= 2) DSK_LIN(2); else if (need <= 3) DSK_LIN(3); else if (need <= 4) DSK_LIN(4);
+  else if (need <= 6) DSK_LIN(6); else DSK_LIN(8);
+#undef DSK_LIN
+}
+
 static int R0(const Model* M, size_t ri) { return M->runs[ri].owner_run; }
 
 static void launch_attn(const float* qa, const float* cache, float* out, int T, int H, int R, const int* ctl, int mask, int window, int ring,
@@ -1009,8 +1139,8 @@ static void enqueue_head(dsk_model* m, dsk_state* s, int first, int count, cudaS
 }
 
 // the model's norm over the T rows of `in` (width values each): stored into `out`, or added into it times alpha (mode 1)
-static void norm_rows(const dsk_hybrid_config& c, State* S, const float* in, const float* w, float* out, int T, int mode, float alpha, cudaStream_t st) {
-  if (c.norm_kind == DSK_NORM_LAYER) layer_norm<<<T, 256, 0, st>>>(in, c.dim, w, out, c.dim, c.dim, c.norm_eps, mode, alpha);
+static void norm_rows(const dsk_hybrid_config& c, State* S, const float* in, const float* w, const float* b, float* out, int T, int mode, float alpha, cudaStream_t st) {
+  if (c.norm_kind == DSK_NORM_LAYER) layer_norm<<<T, 256, 0, st>>>(in, c.dim, w, b, out, c.dim, c.dim, c.norm_eps, mode, alpha);
   else group_rmsnorm<float><<<T, 256, 0, st>>>(in, c.dim, w, out, c.dim, c.dim, c.norm_groups, c.norm_eps, mode, alpha, nullptr, 0);
   S->launches++;
 }
@@ -1068,13 +1198,13 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       if (ty > 1 && c.canon_taps > 1) { canon_history<<<(W + 127) / 128, 128, 0, st>>>(S->x, W, ring, T, W, c.canon_taps, S->d_ctl); S->launches++; }
       return S->h;
     };
-    auto close_post = [&](const HTensor& rg, const float* rg_b, const float* close_w) {
+    auto close_post = [&](const HTensor& rg, const float* rg_b, const float* close_w, const float* close_b) {
       if (c.res_gate) {
         GemmP G = gp(S->x, W, rg.p, W, S->y, W, T, W, W);
         G.bias = rg_b;
         linear(S, bf, HEPI_SIGMUL, G, 1, st);
       }
-      norm_rows(c, S, S->y, close_w, S->x, T, 1, mult, st);
+      norm_rows(c, S, S->y, close_w, close_b, S->x, T, 1, mult, st);
     };
     // decode-sized steps: the closing norm and the next sublayer's input convolution as one kernel (not while the stream is recorded);
     // next_taps / next_ring: the convolution that follows (the feed-forward's, or the next layer's mixer's)
@@ -1097,12 +1227,20 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         add_row<<<T, 256, 0, st>>>(S->x, W, M->loop_step + (size_t)run.pass * W, W);
         S->launches++;
       }
-      norm_rows(c, S, S->x, L.norm1, S->h, T, 0, 0.f, st);
+      norm_rows(c, S, S->x, L.norm1, L.norm1_bias, S->h, T, 0, 0.f, st);
     }
     h_ready = false;
+    const float* hff = hin;   // what a feed-forward of a parallel block reads: the mixer's input ahead of the token shift
+    if (c.token_shift) {      // the mixer reads its input blended with the previous token's; the step's last row is carried on
+      const int ty = (T + kCanonTokens - 1) / kCanonTokens;
+      token_shift<<<dim3((unsigned)((W + 127) / 128), (unsigned)ty), 128, 0, st>>>(hin, W, L.shift, ls.shift, S->hs, W, T, W, S->d_ctl);
+      S->launches++;
+      if (ty > 1) { shift_carry<<<(W + 127) / 128, 128, 0, st>>>(hin, W, ls.shift, T, W); S->launches++; }
+      hin = S->hs;
+    }
     // the closing norm of this run's last sublayer, fused with what opens the next run (its pass vector and first norm) or the head
     auto close_run = [&](const float* wb) {
-      if (!fuse) { norm_rows(c, S, S->y, wb, S->x, T, 1, mult, st); return; }
+      if (!fuse) { norm_rows(c, S, S->y, wb, nullptr, S->x, T, 1, mult, st); return; }
       const Run* next = ri + 1 < M->runs.size() ? &M->runs[ri + 1] : nullptr;
       const float* row = next && next->pass >= 0 ? M->loop_step + (size_t)next->pass * W : nullptr;
       layer_norm_add_norm<<<T, 256, 0, st>>>(S->y, wb, S->x, row, next ? M->L[next->layer].norm1 : M->final_norm, S->h, W, c.norm_eps, mult);
@@ -1113,10 +1251,17 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     if (sp.mixer == DSK_MIX_GQA) {
       const int H = sp.att_heads, G = sp.att_kv_heads, D = sp.att_dim, V = sp.att_vdim, HD = H * D, GD = G * D, GV = G * V, rep = H / G;
       const int keep = sp.att_keep_first;
-      float *kc = (float*)ls.cache, *vc = (float*)ls.vcache;
+      const bool reads = sp.att_kv_from >= 0;   // keys and values of another layer: its caches, written earlier in this step
+      const int ring = M->L[L.owner].ring;
+      float *kc = (float*)S->L[R0(M, ri)].cache, *vc = (float*)S->L[R0(M, ri)].vcache;
       const ScoreMods sm{sp.att_softcap, sp.att_rel_max > 0 ? L.rel : nullptr, L.rel_bucket, sp.att_rel_max, sp.att_sink ? L.sink : nullptr, keep};
       MK("norm");
-      if (sp.att_value_proj) {   // one product for the stacked q / k / v rows; the first value-mixing layer keeps its values for the later ones
+      if (reads) {
+        linear(S, bf, HEPI_STORE, gp(hin, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
+        MK("att.qk");
+        qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, nullptr, nullptr, GD, GV, HD, 0, 0, L.q_norm, nullptr, c.norm_eps, D, sp.rot_dims, L.rot_freq,
+                                        L.rot_mag, S->d_ctl, nullptr, nullptr, ring, keep, nullptr, 0.f, nullptr, sp.rot_layout, sp.att_qk_norm);
+      } else if (sp.att_value_proj) {   // one product for the stacked q / k / v rows; the first value-mixing layer keeps its values for the later ones
         const int ld = HD + GD + GV;
         GemmP P = gp(hin, W, L.qkv.p, W, S->b0, ld, T, ld, W);
         P.bias = sp.att_bias ? L.qkv_b : nullptr;
@@ -1124,14 +1269,14 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         MK("att.qk");
         const bool blend = sp.att_vmix && li != M->vmix_first;
         qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b0 + HD, S->b0 + HD + GD, GD, GV, ld, ld, ld, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims,
-                                        L.rot_freq, L.rot_mag, S->d_ctl, kc, vc, L.ring, keep, blend ? S->vfirst : nullptr, L.vmix,
-                                        sp.att_vmix && li == M->vmix_first ? S->vfirst : nullptr);
+                                        L.rot_freq, L.rot_mag, S->d_ctl, kc, vc, ring, keep, blend ? S->vfirst : nullptr, L.vmix,
+                                        sp.att_vmix && li == M->vmix_first ? S->vfirst : nullptr, sp.rot_layout, sp.att_qk_norm);
       } else {
         linear(S, bf, HEPI_STORE, gp(hin, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
         linear(S, bf, HEPI_STORE, gp(hin, W, L.kproj.p, W, S->b1, GD, T, GD, W), 1, st);
         MK("att.qk");
         qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, S->b1, nullptr, GD, GV, HD, GD, GD, L.q_norm, L.k_norm, c.norm_eps, D, sp.rot_dims, L.rot_freq,
-                                        L.rot_mag, S->d_ctl, kc, vc, L.ring, keep, nullptr, 0.f, nullptr);
+                                        L.rot_mag, S->d_ctl, kc, vc, ring, keep, nullptr, 0.f, nullptr, sp.rot_layout, sp.att_qk_norm);
       }
       S->launches++;
       MK("att.norm+rot");
@@ -1140,7 +1285,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         for (int t0 = 0; t0 < T; t0 += kPrefillQ) {
           const int Tq = std::min(kPrefillQ, T - t0), qpos0 = pos0 + t0;
           const int first = mask_first(sp.att_mask, sp.att_window, qpos0), nk = std::min(keep, first), Lk = nk + qpos0 + Tq - first;
-          pack_ring_kv<float><<<Lk, 256, 0, st>>>(kc, vc, S->kf, S->vf, first, Lk, L.ring, G, D, V, nk, keep);
+          pack_ring_kv<float><<<Lk, 256, 0, st>>>(kc, vc, S->kf, S->vf, first, Lk, ring, G, D, V, nk, keep);
           S->launches++;
           MK("att.pack");
           GemmP Sc = gp(S->b2 + (size_t)t0 * HD, HD, S->kf, D, S->sc, Lk, Tq, Lk, D);
@@ -1164,13 +1309,14 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         }
       } else {
         int NS = 1;
-        if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, L.ring) + keep + 31) / 32, kAttnSplitMax));
+        if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, ring) + keep + 31) / 32, kAttnSplitMax));
         gqa_attn<<<dim3((unsigned)T, (unsigned)NS), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
-            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, L.ring, sp.att_scale, NS, S->part, sm);
+            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, ring, sp.att_scale, NS, S->part, sm);
         if (NS > 1) latent_swa_merge<<<dim3((unsigned)(T * H), (unsigned)((V + 127) / 128)), 128, 0, st>>>(S->part, S->b3, V, NS);
         S->launches += NS > 1 ? 2 : 1;
         MK("att.decode");
       }
+      if (sp.att_out_gate) linear(S, bf, HEPI_SIGMUL, gp(hin, W, L.gmat.p, W, S->b3, H * V, T, H * V, W), 1, st);   // heads *= sigmoid(g h)
       GemmP P = gp(S->b3, H * V, L.o.p, H * V, sink.C, W, T, W, H * V);
       P.alpha = sink.alpha;
       linear(S, bf, sink.epi, P, 1, st);
@@ -1239,6 +1385,22 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       P.alpha = sink.alpha;
       linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
+    } else if (sp.mixer == DSK_MIX_HGRN2) {
+      const int H = sp.lin_heads, HN = H * sp.lin_dim, HP = H * sp.lin_vdim, pw = 2 * HN + HP;
+      MK("norm");
+      GemmP In = gp(hin, W, L.lin_in.p, W, S->b0, pw, T, pw, W);   // [raw q | raw forget gate (+ bias) | v]
+      In.bias = L.lin_bias;
+      linear(S, bf, HEPI_STORE, In, 1, st);
+      MK("lin.in");
+      launch_hgrn2(sp, S->b0, pw, L.lower, ls.lin, S->b2, T, st);
+      MK("lin.scan");
+      group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, HP, L.lin_norm, S->b3, HP, HP, H, c.norm_eps, 0, 0.f, nullptr, 0);
+      S->launches += 2;
+      MK("lin.norm");
+      GemmP P = gp(S->b3, HP, L.o.p, HP, sink.C, W, T, W, HP);
+      P.alpha = sink.alpha;
+      linear(S, bf, sink.epi, P, 1, st);
+      MK("lin.o");
     } else if (is_ssd(sp)) {
       const int inner = (int)ssd_inner(sp), ch = (int)ssd_channels(sp), pw = (int)ssd_proj(sp);
       MK("norm");
@@ -1318,11 +1480,12 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       linear(S, bf, sink.epi, P, 1, st);
       MK("att.o");
     }
+    if (!post) hin = hff;
     if (post) {   // the mixer's result closes; the feed-forward (or, without one, the next layer's mixer) opens on the new stream
       if (small_post && sp.ff_kind != DSK_FF_NONE) { close_open(L.rg1, L.rg1_b, L.close1, L.canon2, ring_of(ri, 1)); hin = S->h; }
       else if (small_post && has_next) { close_open(L.rg1, L.rg1_b, L.close1, M->L[M->runs[ri + 1].layer].canon1, ring_of(ri + 1, 0)); h_ready = true; }
       else {
-        close_post(L.rg1, L.rg1_b, L.close1);
+        close_post(L.rg1, L.rg1_b, L.close1, L.norm1_bias);
         if (sp.ff_kind != DSK_FF_NONE) hin = open_post(L.canon2, 1);
       }
       MK("norm");
@@ -1333,8 +1496,8 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         layer_norm_add_norm<<<T, 256, 0, st>>>(S->y, L.norm1b, S->x, nullptr, L.norm2, S->h, W, c.norm_eps, mult);
         S->launches++;
       } else {
-        norm_rows(c, S, S->y, L.norm1b, S->x, T, 1, mult, st);
-        norm_rows(c, S, S->x, L.norm2, S->h, T, 0, 0.f, st);
+        norm_rows(c, S, S->y, L.norm1b, nullptr, S->x, T, 1, mult, st);
+        norm_rows(c, S, S->x, L.norm2, nullptr, S->h, T, 0, 0.f, st);
       }
       MK("norm");
     }
@@ -1361,17 +1524,22 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     if (sp.ff_kind == DSK_FF_MOE) {
       const int E = sp.ff_experts, top = sp.ff_top, ff = sp.ff_hidden, pairs = T * top;
-      linear(S, false, HEPI_STORE, gp(hin, W, L.router, W, S->b0, E, T, E, W), 1, st);   // router: fp32 weights in every mode
-      moe_route<<<T, 128, (size_t)(2 * E + top) * 4, st>>>(S->b0, L.correction, E, top, sp.ff_router_scale, S->d_idx, S->wgt);
+      GemmP Rt = gp(hin, W, L.router, W, S->b0, E, T, E, W);   // router: fp32 weights in every mode
+      Rt.bias = sp.ff_router == DSK_ROUTER_TOP_SOFTMAX ? L.router_b : nullptr;
+      linear(S, false, HEPI_STORE, Rt, 1, st);
+      moe_route<<<T, 128, (size_t)(2 * E + top) * 4, st>>>(S->b0, sp.ff_router == DSK_ROUTER_SIGMOID ? L.correction : nullptr, E, top, sp.ff_router_scale, S->d_idx,
+                                                           S->wgt, sp.ff_router == DSK_ROUTER_TOP_SOFTMAX ? 1 : 0);
       S->launches++;
       MK("moe.router");
-      GemmP G = gp(hin, W, L.gate_s.p, W, S->b2, ff, pairs, ff, W);
-      G.W2 = L.up_s.p; G.sW = (long long)ff * W; G.lim = sp.ff_limit;
+      const bool relu2 = sp.ff_expert == DSK_EXPERT_RELU2;   // one up matrix per expert instead of a gated pair
+      const int epi_up = relu2 ? HEPI_RELU2 : HEPI_GLU;
+      GemmP G = gp(hin, W, relu2 ? L.up_s.p : L.gate_s.p, W, S->b2, ff, pairs, ff, W);
+      G.W2 = relu2 ? nullptr : L.up_s.p; G.sW = (long long)ff * W; G.lim = sp.ff_limit;
       GemmP Dn = gp(S->b2, ff, L.down_s.p, ff, S->b3, W, pairs, W, ff);
       Dn.sW = (long long)ff * W;
       if (T <= 4) {
         G.z_expert = S->d_idx; G.z_adiv = top; Dn.z_expert = S->d_idx; Dn.z_adiv = 1;
-        linear(S, bf, HEPI_GLU, G, pairs, st);
+        linear(S, bf, epi_up, G, pairs, st);
         MK("moe.glu");
         linear(S, bf, HEPI_STORE, Dn, pairs, st);
         MK("moe.down");
@@ -1383,7 +1551,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         Dn.tiles = S->d_tiles; Dn.n_tiles = S->d_ntiles; Dn.a_map = S->d_perm; Dn.a_div = 1; Dn.c_map = S->d_perm;
         const int cap = std::min(S->max_tiles, pairs / bm + E + 1);
         MK("moe.plan");
-        linear(S, bf, HEPI_GLU, G, 1, st, cap);
+        linear(S, bf, epi_up, G, 1, st, cap);
         MK("moe.glu");
         linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
         MK("moe.down");
@@ -1398,7 +1566,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     if (post && sp.ff_kind != DSK_FF_NONE) {
       if (small_post && has_next) { close_open(L.rg2, L.rg2_b, L.close2, M->L[M->runs[ri + 1].layer].canon1, ring_of(ri + 1, 0)); h_ready = true; }
-      else close_post(L.rg2, L.rg2_b, L.close2);
+      else close_post(L.rg2, L.rg2_b, L.close2, L.norm2_bias);
       MK("norm");
     }
     if (c.side_dim > 0) {
@@ -1414,7 +1582,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     if (trace) CKL(cudaMemcpyAsync(trace + ri * (size_t)T * W, S->x, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, st));
   }
   if (n_want > 0) {   // final norm of every row, LM head on the first group of wanted rows (enqueue_head does the others)
-    if (!h_ready) norm_rows(c, S, S->x, M->final_norm, S->h, T, 0, 0.f, st);
+    if (!h_ready) norm_rows(c, S, S->x, M->final_norm, M->final_norm_b, S->h, T, 0, 0.f, st);
     enqueue_head(m, s, 0, std::min(n_want, S->head_rows), st);
     MK("head");
   }

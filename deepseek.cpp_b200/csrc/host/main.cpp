@@ -271,10 +271,66 @@ static bool sakusun_config_from(const JValue& j, const std::string& quant, int c
   return true;
 }
 
+// The Nalizen design: post-norm blocks whose layer norms carry a bias, a token shift in front of every mixer, a scaled embedding that
+// is also the head, the per-layer token input; grouped-query attention (half-split rotation with wavelength-band scaling, per-head
+// query / key norm after the rotation, sliding window, output gate, optionally another layer's keys and values) or the HGRN2
+// recurrence; gated dense feed-forwards or routed ones (largest logits, softmax over the chosen, squared-ReLU experts).
+static bool nalizen_config_from(const JValue& j, const std::string& quant, int context, dsk_hybrid_config* hc, std::vector<dsk_layer_spec>* specs) {
+  const JValue& layers = j.at("layers");
+  if (layers.kind != JValue::Arr || layers.arr.empty()) { fprintf(stderr, "FATAL: config.json has no layers\n"); return false; }
+  *hc = dsk_hybrid_config{};
+  hc->dim = j.integer("width", 0); hc->vocab_size = j.integer("vocab", 0); hc->n_layers = (int)layers.arr.size();
+  hc->max_seq_len = context > 0 ? context : 1 << 30;
+  hc->quant = quant == "fp32" ? DSK_F32 : DSK_BF16;
+  hc->chunk = context > 0 ? std::min(256, context) : 256;
+  hc->norm_eps = (float)j.at("norm").number("eps", 1e-5); hc->norm_groups = 1;
+  hc->residual_mult = 1.f; hc->logit_scale = 1.f;
+  hc->side_dim = j.at("token_side").integer("dim", 0);
+  hc->block = DSK_BLOCK_POST; hc->norm_kind = DSK_NORM_LAYER; hc->norm_bias = 1; hc->tie_head = 1; hc->token_shift = 1;
+  hc->embed_scale = (float)j.at("embedding").number("scale", 1.0);
+  for (size_t i = 0; i < layers.arr.size(); i++) {
+    const JValue& lc = layers.arr[i];
+    const JValue& mx = lc.at("mixer");
+    const std::string type = lc.at("type").str;
+    dsk_layer_spec sp{};
+    sp.att_kv_from = -1;
+    if (type == "attention") {
+      sp.mixer = DSK_MIX_GQA;
+      sp.att_heads = mx.integer("heads", 0); sp.att_kv_heads = mx.integer("kv_heads", sp.att_heads);
+      sp.att_dim = mx.integer("dim", 0); sp.att_vdim = mx.integer("vdim", 0); sp.att_scale = (float)mx.number("scale", 1.0);
+      sp.att_mask = DSK_MASK_WINDOW; sp.att_window = mx.at("mask").integer("size", 1 << 30);
+      sp.att_value_proj = 1; sp.att_out_gate = 1; sp.att_qk_norm = DSK_QKNORM_HEAD;
+      sp.att_kv_from = mx.integer("kv_from", -1);
+      const JValue& rot = mx.at("rot");
+      sp.rot_dims = rot.integer("dims", 0); sp.rot_base = (float)rot.number("base", 10000.0); sp.rot_layout = DSK_ROT_HALF;
+      if (rot.has("scaling")) {
+        const JValue& sc = rot.at("scaling");
+        sp.rot_scale = DSK_ROTSCALE_BANDS; sp.rot_factor = (float)sc.number("factor", 0.0); sp.rot_original = sc.integer("original", 0);
+        sp.rot_fast = (float)sc.number("high", 0.0); sp.rot_slow = (float)sc.number("low", 0.0);
+        if (!(sp.rot_factor > 0.f)) { fprintf(stderr, "FATAL: layer %zu: rotation scaling factor must be positive\n", i); return false; }
+      }
+    } else if (type == "hgrn2") {
+      sp.mixer = DSK_MIX_HGRN2;
+      sp.lin_heads = mx.integer("heads", 0); sp.lin_dim = mx.integer("dim", 0); sp.lin_vdim = mx.integer("vdim", 0);
+    } else { fprintf(stderr, "FATAL: layer %zu: unknown mixer type %s\n", i, type.c_str()); return false; }
+    if (lc.has("mlp")) {
+      const JValue& ff = lc.at("mlp");
+      const std::string kind = ff.at("kind").str;
+      if (kind == "dense") { sp.ff_kind = DSK_FF_DENSE; sp.ff_hidden = ff.integer("ff", 0); sp.ff_act = DSK_ACT_GEGLU; }
+      else if (kind == "moe") {
+        sp.ff_kind = DSK_FF_MOE; sp.ff_router = DSK_ROUTER_TOP_SOFTMAX; sp.ff_expert = DSK_EXPERT_RELU2; sp.ff_router_scale = 1.f;
+        sp.ff_experts = ff.at("router").integer("experts", 0); sp.ff_top = ff.at("router").integer("top", 0); sp.ff_hidden = ff.at("expert").integer("ff", 0);
+      } else { fprintf(stderr, "FATAL: layer %zu: unknown feed-forward kind %s\n", i, kind.c_str()); return false; }
+    }
+    specs->push_back(sp);
+  }
+  return true;
+}
+
 // config.json "architecture" -> builder of the C-ABI model description
 typedef bool (*ArchBuilder)(const JValue&, const std::string&, int, dsk_hybrid_config*, std::vector<dsk_layer_spec>*);
 static const struct { const char* name; ArchBuilder build; } kArchitectures[] = {{"Desarax", hybrid_config_from}, {"Rutulix", rutulix_config_from},
-                                                                                {"Sakusun", sakusun_config_from}};
+                                                                                {"Sakusun", sakusun_config_from}, {"Nalizen", nalizen_config_from}};
 
 // completion over token ids: the prompt goes through dsk_forward_chunk (prefill in portions), then the usual
 // dsk_sample -> dsk_forward loop; the ids are printed (these checkpoints carry no tokenizer).
@@ -288,7 +344,7 @@ static int run_layer_list(const std::string& dir, const std::string& quant, cons
   const std::string arch = cfg.at("architecture").str;
   ArchBuilder builder = nullptr;
   for (const auto& a : kArchitectures) if (arch == a.name) builder = a.build;
-  if (!builder) { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax, Rutulix, Sakusun)\n", arch.c_str()); return 1; }
+  if (!builder) { fprintf(stderr, "FATAL: unknown architecture '%s' (known: Desarax, Rutulix, Sakusun, Nalizen)\n", arch.c_str()); return 1; }
   if (quant != "bf16" && quant != "fp32") { fprintf(stderr, "FATAL: -q must be bf16 or fp32\n"); return 1; }
   std::vector<int> enc;
   for (size_t i = 0; i < prompt_ids.size();) {

@@ -23,12 +23,17 @@ sys.path.insert(0, HERE)
 import dseek  # noqa: E402
 
 QUANT_IDS = {"fp32": 0, "fp16": 1, "f8e5m2": 2, "q2_k": 3, "q3_k": 4, "bf16": 5}
-MIX_SSD, MIX_LATENT_SWA, MIX_GQA, MIX_MLA = 0, 1, 2, 3
+MIX_SSD, MIX_LATENT_SWA, MIX_GQA, MIX_MLA, MIX_HGRN2 = 0, 1, 2, 3, 4
 FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
 MASK_WINDOW, MASK_CHUNK = 0, 1
 ACT_XIELU, ACT_GEGLU = 0, 1
 BLOCK_PARALLEL, BLOCK_SANDWICH, BLOCK_POST = 0, 1, 2
 NORM_RMS, NORM_LAYER = 0, 1
+ROT_PAIRS, ROT_HALF = 0, 1
+ROTSCALE_YARN, ROTSCALE_BANDS = 0, 1
+QKNORM_WHOLE, QKNORM_HEAD = 0, 1
+ROUTER_SIGMOID, ROUTER_TOP_SOFTMAX = 0, 1
+EXPERT_GLU_CLAMPED, EXPERT_RELU2 = 0, 1
 HYDRATE_KV_CACHE, OUTPUT_LOGITS = 0, 1
 
 f32p = C.POINTER(C.c_float)
@@ -96,7 +101,9 @@ class LayerSpec(C.Structure):
                [(n, C.c_int) for n in ("att_mask", "att_kv_heads", "att_talk", "rot_dims", "rot_original")] + \
                [(n, C.c_float) for n in ("rot_base", "rot_factor", "rot_fast", "rot_slow")] + [("ff_act", C.c_int)] + \
                [(n, C.c_int) for n in ("att_value_proj", "att_bias", "att_keep_first", "att_rel_max", "att_sink", "att_vmix")] + \
-               [("att_softcap", C.c_float)] + [(n, C.c_int) for n in ("att_q_rank", "att_rot_dim", "att_out_gate")]
+               [("att_softcap", C.c_float)] + \
+               [(n, C.c_int) for n in ("att_q_rank", "att_rot_dim", "att_out_gate", "rot_layout", "rot_scale", "att_qk_norm",
+                                       "lin_heads", "lin_dim", "lin_vdim", "ff_router", "ff_expert")]
 
 
 class HybridConfig(C.Structure):
@@ -106,7 +113,8 @@ class HybridConfig(C.Structure):
                 ("side_dim", C.c_int)] + \
                [(n, C.c_int) for n in ("block", "norm_kind", "tie_head", "loop_start", "loop_stop", "loop_times")] + \
                [("embed_scale", C.c_float)] + \
-               [(n, C.c_int) for n in ("bigram_buckets", "bigram_mul_prev", "bigram_mul_cur", "norm_scalar", "canon_taps", "res_gate", "layer_scale")]
+               [(n, C.c_int) for n in ("bigram_buckets", "bigram_mul_prev", "bigram_mul_cur", "norm_scalar", "canon_taps", "res_gate", "layer_scale",
+                                       "norm_bias", "token_shift")]
 
 
 # mixer "type" strings of a layer-list config.json -> mixer kernel family.  Two names may map to one mechanism.
@@ -266,11 +274,69 @@ def sakusun_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, ch
     return hc, specs
 
 
+def nalizen_from_config(cfg: dict, quant: str = "bf16", max_seq_len: int = 0, chunk: int = 256):
+    """config.json of the Nalizen design -> (HybridConfig, LayerSpec array): post-norm blocks whose layer norms carry a bias, a
+    token shift in front of every mixer, a scaled embedding that is also the head, the per-layer token input, and per layer either
+    grouped-query attention (half-split rotation with wavelength-band scaling, per-head query / key norm after the rotation,
+    sliding window, output gate, optionally the keys and values of an earlier layer) or the HGRN2 recurrence; gated dense
+    feed-forwards or routed ones (largest logits, softmax over the chosen, squared-ReLU experts).  Absent keys switch a part off."""
+    hc = HybridConfig()
+    layers = cfg["layers"]
+    hc.dim, hc.vocab_size, hc.n_layers = int(cfg["width"]), int(cfg["vocab"]), len(layers)
+    hc.quant, hc.chunk = QUANT_IDS[quant], int(chunk)
+    hc.max_seq_len = int(max_seq_len) if max_seq_len else 1 << 30
+    hc.norm_eps, hc.norm_groups = float(cfg["norm"]["eps"]), 1
+    hc.residual_mult, hc.logit_scale = 1.0, 1.0
+    hc.side_dim = int((cfg.get("token_side") or {}).get("dim", 0))
+    hc.block, hc.norm_kind, hc.norm_bias, hc.tie_head, hc.token_shift = BLOCK_POST, NORM_LAYER, 1, 1, 1
+    hc.embed_scale = float((cfg.get("embedding") or {}).get("scale", 1.0))
+    specs = (LayerSpec * len(layers))()
+    for i, lc in enumerate(layers):
+        sp, mx = specs[i], lc["mixer"]
+        sp.att_kv_from = -1
+        if lc["type"] == "attention":
+            sp.mixer = MIX_GQA
+            sp.att_heads, sp.att_kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
+            sp.att_dim, sp.att_vdim, sp.att_scale = int(mx["dim"]), int(mx["vdim"]), float(mx["scale"])
+            mask = mx.get("mask") or {}
+            sp.att_mask = MASK_WINDOW
+            sp.att_window = int(mask["size"]) if "size" in mask else 1 << 30      # no window: every earlier token is visible
+            sp.att_value_proj, sp.att_out_gate, sp.att_qk_norm = 1, 1, QKNORM_HEAD
+            sp.att_kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
+            rot = mx.get("rot") or {}
+            sp.rot_dims, sp.rot_base, sp.rot_layout = int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), ROT_HALF
+            sc = rot.get("scaling")
+            if sc:
+                sp.rot_scale, sp.rot_factor, sp.rot_original = ROTSCALE_BANDS, float(sc["factor"]), int(sc["original"])
+                sp.rot_fast, sp.rot_slow = float(sc["high"]), float(sc["low"])
+                if not sp.rot_factor > 0:
+                    raise DskError(f"layer {i}: rotation scaling factor must be positive")
+            else:
+                sp.rot_factor = 0.0
+        elif lc["type"] == "hgrn2":
+            sp.mixer = MIX_HGRN2
+            sp.lin_heads, sp.lin_dim, sp.lin_vdim = int(mx["heads"]), int(mx["dim"]), int(mx["vdim"])
+        else:
+            raise DskError(f"layer {i}: unknown mixer type {lc['type']!r}")
+        ff = lc.get("mlp")
+        if not ff:
+            sp.ff_kind = FF_NONE
+        elif ff.get("kind") == "dense":
+            sp.ff_kind, sp.ff_hidden, sp.ff_act = FF_DENSE, int(ff["ff"]), ACT_GEGLU
+        elif ff.get("kind") == "moe":
+            sp.ff_kind, sp.ff_router, sp.ff_expert = FF_MOE, ROUTER_TOP_SOFTMAX, EXPERT_RELU2
+            sp.ff_experts, sp.ff_top, sp.ff_hidden = int(ff["router"]["experts"]), int(ff["router"]["top"]), int(ff["expert"]["ff"])
+            sp.ff_router_scale = 1.0
+        else:
+            raise DskError(f"layer {i}: unknown feed-forward kind {ff.get('kind')!r}")
+    return hc, specs
+
+
 # config.json "architecture" -> builder of the C-ABI model description (the DeepSeek families come as .dseek metadata instead)
-ARCHITECTURES = {"Desarax": hybrid_from_config, "Rutulix": rutulix_from_config, "Sakusun": sakusun_from_config}
+ARCHITECTURES = {"Desarax": hybrid_from_config, "Rutulix": rutulix_from_config, "Sakusun": sakusun_from_config, "Nalizen": nalizen_from_config}
 
 _lib = None
-ABI_VERSION = 6   # DSK_ABI_VERSION (include/dsk.h)
+ABI_VERSION = 7   # DSK_ABI_VERSION (include/dsk.h)
 
 
 def build(force: bool = False) -> str:

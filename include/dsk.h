@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define DSK_ABI_VERSION 6
+#define DSK_ABI_VERSION 7
 
 /* Quant: src/codec.h:79-85 (same numbering) */
 enum { DSK_F32 = 0, DSK_F16 = 1, DSK_F8E5M2 = 2, DSK_Q2_K = 3, DSK_Q3_K = 4,
@@ -68,8 +68,11 @@ typedef struct dsk_config {
  * (That is DSK_BLOCK_PARALLEL with DSK_NORM_RMS, the Desarax design; the Rutulix design is DSK_BLOCK_SANDWICH with
  * DSK_NORM_LAYER, DSK_MIX_GQA mixers, DSK_FF_DENSE feed-forwards, an untied head and a layer loop; the Sakusun design is
  * DSK_BLOCK_POST with single-number RMS norms, DSK_MIX_GQA mixers with their switches on or DSK_MIX_MLA mixers, gated
- * DSK_FF_DENSE feed-forwards, a scaled embedding plus bigram table and an untied head.) */
-enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2, DSK_MIX_MLA = 3 };
+ * DSK_FF_DENSE feed-forwards, a scaled embedding plus bigram table and an untied head; the Nalizen design is DSK_BLOCK_POST with
+ * layer norms that carry a bias, a token shift in front of every mixer, DSK_MIX_GQA mixers (half-split rotation with wavelength-band
+ * scaling, per-head query / key norm after the rotation, output gate, shared key / value caches) or DSK_MIX_HGRN2 mixers, gated dense
+ * or DSK_ROUTER_TOP_SOFTMAX / DSK_EXPERT_RELU2 routed feed-forwards, a scaled and tied embedding and the per-layer token input.) */
+enum { DSK_MIX_SSD = 0, DSK_MIX_LATENT_SWA = 1, DSK_MIX_GQA = 2, DSK_MIX_MLA = 3, DSK_MIX_HGRN2 = 4 };
 enum { DSK_FF_NONE = 0, DSK_FF_MOE = 1, DSK_FF_DENSE = 2 };
 enum { DSK_MASK_WINDOW = 0,   /* position i sees j with 0 <= i - j < att_window */
        DSK_MASK_CHUNK = 1 };  /* position i sees j <= i with floor(i / att_window) == floor(j / att_window): borders at multiples of att_window in sequence positions */
@@ -81,7 +84,18 @@ enum { DSK_BLOCK_PARALLEL = 0,   /* h = norm1(x); x += residual_mult (mixer(h) +
                                     u = x + conv(x) (canon_taps > 0; else u = x);  y = f(u) (* sigmoid(rg x + rg.b) with res_gate);
                                     x += norm(y) (* ls with layer_scale), for f = mixer (tensors norm1, canon1, rg1, ls1), then feed-forward (..2) */
 enum { DSK_NORM_RMS = 0,         /* x / sqrt(mean(x^2) + eps) * w in norm_groups parts */
-       DSK_NORM_LAYER = 1 };     /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, no bias */
+       DSK_NORM_LAYER = 1 };     /* (x - mean) / sqrt(mean((x - mean)^2) + eps) * w (+ b with dsk_hybrid_config::norm_bias: tensor <norm>.b) */
+enum { DSK_ROT_PAIRS = 0,        /* entries (2i, 2i + 1) of a head turn together */
+       DSK_ROT_HALF = 1 };       /* entries (i, i + rot_dims / 2) of a head turn together */
+enum { DSK_ROTSCALE_YARN = 0,    /* rot_factor > 0: YaRN ramp between rot_fast and rot_slow turns per rot_original positions, magnitude 0.1 ln(factor) + 1 */
+       DSK_ROTSCALE_BANDS = 1 }; /* rot_factor > 0: by wavelength l = 2 pi / f: f kept where l < rot_original / rot_fast, f / rot_factor where
+                                    l > rot_original / rot_slow, between them (1 - s) f / rot_factor + s f with s = (rot_original / l - rot_slow) / (rot_fast - rot_slow) */
+enum { DSK_QKNORM_WHOLE = 0,     /* RMS norm with weights mix.q.norm / mix.k.norm over the whole projection, before the rotation */
+       DSK_QKNORM_HEAD = 1 };    /* every head of q and k divided by its own RMS after the rotation, no weight */
+enum { DSK_ROUTER_SIGMOID = 0,   /* sigmoid scores, selection by score + mlp.correction, weights = chosen scores normalised x ff_router_scale */
+       DSK_ROUTER_TOP_SOFTMAX = 1 };   /* logits = router h + mlp.router.b; the ff_top largest logits; weights = softmax over the chosen logits */
+enum { DSK_EXPERT_GLU_CLAMPED = 0,     /* down(g sigmoid(1.702 g) (u + 1)), g = min(gate h, limit), u = clamp(up h, +-limit) */
+       DSK_EXPERT_RELU2 = 1 };         /* down(max(up h, 0)^2), no gate matrix */
 /* DSK_MIX_GQA also has these switches (all off in the Rutulix design): att_value_proj (values = v matrix mix.v of att_vdim per
  * key head instead of the raw key projection), att_bias (biases mix.q.b / k.b / v.b added in the projections), att_softcap > 0
  * (score <- cap tanh(score / cap) after the scale), att_rel_max > 0 (a learned bias per distance bucket and head added after
@@ -103,6 +117,14 @@ enum { DSK_NORM_RMS = 0,         /* x / sqrt(mean(x^2) + eps) * w in norm_groups
  *                       rot_original / wavelength = rot_fast and rot_slow; cos and sin times 0.1 ln(rot_factor) + 1); scores times
  *                       att_scale; with att_talk the heads' scores are mixed before the softmax (score_h <- sum_g T[h][g] score_g,
  *                       tensor mix.talk); mask att_mask of size att_window.  Carries a ring of keys and values per layer run.
+ *                       More switches (off in the older designs): rot_layout, rot_scale, att_qk_norm, att_out_gate (heads multiplied by
+ *                       sigmoid(g h), tensor mix.g, before the output projection) and att_kv_from >= 0: the layer has no key / value
+ *                       projections and reads the caches of that earlier DSK_MIX_GQA layer (prepared keys and values as cached there)
+ *                       with its own queries, mask and scale; head counts, sizes and rotation must equal the owner's.
+ *   DSK_MIX_HGRN2       gated linear recurrence per head: q = silu(q h) [lin_heads][lin_dim], v = v h [lin_heads][lin_vdim], forget gate
+ *                       f = l + (1 - l) sigmoid(f h + f.b) with the lower bound l = tensor mix.lower; S <- diag(f) S + (1 - f) v^T,
+ *                       o = S^T q; every head's o is RMS-normed with the weight mix.norm [lin_vdim] shared by the heads; output projection
+ *                       mix.o.  Carries S [lin_heads][lin_dim][lin_vdim] in fp32 per sequence.
  *   DSK_FF_DENSE        down(act(up h + b_up)) + b_down with activation ff_act. */
 typedef struct dsk_layer_spec {
   int mixer;                                                            /* DSK_MIX_* */
@@ -119,6 +141,9 @@ typedef struct dsk_layer_spec {
   int att_value_proj, att_bias, att_keep_first, att_rel_max, att_sink, att_vmix;   /* DSK_MIX_GQA switches (above) */
   float att_softcap;
   int att_q_rank, att_rot_dim, att_out_gate;                            /* DSK_MIX_MLA (with att_heads, att_dim, att_vdim, att_kv_rank, att_scale, att_mask, att_window, rot_dims, rot_base) */
+  int rot_layout, rot_scale, att_qk_norm;                               /* DSK_MIX_GQA: DSK_ROT_*, DSK_ROTSCALE_*, DSK_QKNORM_* */
+  int lin_heads, lin_dim, lin_vdim;                                     /* DSK_MIX_HGRN2 */
+  int ff_router, ff_expert;                                             /* DSK_FF_MOE: DSK_ROUTER_*, DSK_EXPERT_* */
 } dsk_layer_spec;
 typedef struct dsk_hybrid_config {
   int dim, vocab_size, n_layers;
@@ -141,6 +166,9 @@ typedef struct dsk_hybrid_config {
   int norm_scalar;           /* 1: the weights of the norms outside the mixers (norm1, norm2, final.norm) are single numbers */
   int canon_taps, res_gate, layer_scale;   /* DSK_BLOCK_POST: taps of the causal per-channel input convolution (tensors canon1 / canon2 [dim][taps], last tap on
                                               the current token; 0: none), gated sublayer results (rg1 / rg2 [dim][dim] + .b), per-channel scale after the norm (ls1 / ls2) */
+  int norm_bias;             /* DSK_NORM_LAYER: every norm outside the mixers adds a bias, tensor "<norm>.b" */
+  int token_shift;           /* 1: a mixer reads h + (h' - h) * shift (tensor l<i>.shift [dim]) instead of its input h, h' being the previous token's h
+                                (zeros for the first token of a sequence); the last h of every layer run is part of the sequence's state */
 } dsk_hybrid_config;
 
 typedef struct dsk_model dsk_model;
