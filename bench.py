@@ -613,7 +613,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the V2-Lite configs[1]/[2] continuity numbers")
     ap.add_argument("--profile-token", action="store_true", help="print the per-stage timeline of one token to stderr")
     ap.add_argument("--hybrid", default="", help="instead of the headline workload: prefill / decode throughput of the layer-list family "
-                    "beside the closest existing model at equal size (Desarax sizes: a DeepSeek true-MLA model; rutulix_* sizes: a Desarax model; sakusun_* sizes: a Rutulix model); "
+                    "beside the closest existing model at equal size (Desarax sizes: a DeepSeek true-MLA model; rutulix_* sizes: a Desarax model; sakusun_* sizes: a Rutulix model; nalizen_* sizes: a Desarax model); "
                     "comma-separated sizes of hybrid_bench.SIZES, or 'all'")
     a = ap.parse_args()
     if a.hybrid:

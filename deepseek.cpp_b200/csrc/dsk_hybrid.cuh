@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(256) group_rmsnorm(const float* __restrict__ i
 // ---------------------------------------------------------------------------------------------------------------------
 // matrix products
 // ---------------------------------------------------------------------------------------------------------------------
-enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4, HEPI_GEGLU = 5, HEPI_SIGMUL = 6, HEPI_RELU2 = 7 };
+enum { HEPI_STORE = 0, HEPI_ADD = 1, HEPI_GLU = 2, HEPI_GELU_MUL = 3, HEPI_XIELU = 4, HEPI_GEGLU = 5, HEPI_SIGMUL = 6, HEPI_RELU2 = 7, HEPI_LINGATE = 8 };
 __host__ __device__ constexpr bool epi_dual(int epi) { return epi == HEPI_GLU || epi == HEPI_GEGLU; }   // two weight matrices per output
 
 struct GemmP {
@@ -231,7 +231,8 @@ struct GemmP {
   float alpha;             // STORE: C = alpha acc; ADD: C += alpha acc
   float lim;               // GLU: g = min(gate, lim), u = clamp(up, -lim, lim), C = g sigmoid(1.702 g) (u + 1)
                            // GEGLU: C = gelu_tanh(gate) * up;  SIGMUL: C *= sigmoid(acc) (a gate on what C already holds);
-                           // RELU2: C = max(acc, 0)^2
+                           // RELU2: C = max(acc, 0)^2;  LINGATE (the stacked [q | f | v] projection of a gated linear recurrence, aux_off
+                           // columns of q and of f): q columns silu(acc), f columns l + (1 - l) sigmoid(acc) with l = aux[n - aux_off] (fp32), v columns acc
   const void* aux;         // GELU_MUL: C = gelu_tanh(acc) * aux[aux_row[row] * aux_ld + aux_off + n]
   const int* aux_row;
   int aux_ld, aux_off;
@@ -248,6 +249,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmP& P, float* __restrict_
   else if (EPI == HEPI_GEGLU) crow[n] = gelu_tanh_f(v) * v2;
   else if (EPI == HEPI_SIGMUL) crow[n] *= sigmoid_f(v);
   else if (EPI == HEPI_RELU2) { const float r = fmaxf(v, 0.f); crow[n] = r * r; }
+  else if (EPI == HEPI_LINGATE) {
+    const int hn = P.aux_off;
+    if (n < hn) crow[n] = silu_f(v);
+    else if (n < 2 * hn) { const float lo = reinterpret_cast<const float*>(P.aux)[n - hn]; crow[n] = fmaf(1.f - lo, sigmoid_f(v), lo); }
+    else crow[n] = v;
+  }
   else if (EPI == HEPI_GLU) {
     const float g = fminf(v, P.lim), u = fminf(fmaxf(v2, -P.lim), P.lim);
     crow[n] = g * sigmoid_f(1.702f * g) * (u + 1.f);
@@ -858,15 +865,15 @@ __global__ void shift_carry(const float* __restrict__ x, int ld, float* __restri
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Gated linear recurrence (HGRN2 form) over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens:
-//   f = l + (1 - l) sigmoid(raw_f)   per head and key channel n (l: lower bound);   q = silu(raw_q);
 //   S[n][p] <- f[n] S[n][p] + (1 - f[n]) v[p]   (computed as v + f (S - v));   o[p] = sum_n q[n] S[n][p]
-// proj rows hold [raw_q | raw_f | v] at the given offsets (H * N, H * N, H * P wide); state [H][N][P] fp32.  Thread (pl, s) owns
-// value channel p = p0 + pl and 4 RQ rows n = 4 (s + 8 j) + k of S[:, p] in registers; the eight threads of a channel reduce o with
-// shuffles.  Gates and queries of TB tokens at a time are computed while they are staged, off the sequential path.
+// proj rows hold [q | f | v] at the given offsets (H * N, H * N, H * P wide) with the activations already applied by the
+// projection's epilogue: q = silu(.), f = l + (1 - l) sigmoid(.) in fp32.  state [H][N][P] fp32.  Thread (pl, s) owns value channel
+// p = p0 + pl and 4 RQ rows n = 4 (s + 8 j) + k of S[:, p] in registers; the eight threads of a channel reduce o with shuffles.
+// Inputs of TB tokens at a time are staged in shared memory.
 // ---------------------------------------------------------------------------------------------------------------------
 template <int RQ>
 __global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
-                                                  const float* __restrict__ lower, float* __restrict__ state, float* __restrict__ out,
+                                                  float* __restrict__ state, float* __restrict__ out,
                                                   int ld_out, int T, int H, int N, int P, int PB, int TB) {
   extern __shared__ __align__(16) float sm[];
   const int NP = (N + 3) & ~3;      // staged rows are padded to whole float4s
@@ -888,25 +895,19 @@ __global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj
     const int nt = min(TB, T - t0);
     __syncthreads();
     for (int base = 0; base < nt * NP; base += 4 * (int)blockDim.x) {   // four elements per thread and pass: eight loads in flight
-      float rf[4], rq[4], lo[4];
+      float rf[4], rq[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const int i = base + u * (int)blockDim.x + tid;
         const int tt = i / NP, n = i - tt * NP;
-        const bool ok = i < nt * NP && n < N;
+        const bool ok = i < nt * NP && n < N;      // padding rows: f = 0, q = 0 (they never reach the output or the stored state)
         rf[u] = ok ? proj[(size_t)(t0 + tt) * ld + f_off + h * N + n] : 0.f;
         rq[u] = ok ? proj[(size_t)(t0 + tt) * ld + q_off + h * N + n] : 0.f;
-        lo[u] = ok ? lower[h * N + n] : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const int i = base + u * (int)blockDim.x + tid;
-        const int tt = i / NP, n = i - tt * NP;
-        if (i < nt * NP) {
-          const bool ok = n < N;     // padding rows: f = 0, q = 0 (they never reach the output or the stored state)
-          s_f[i] = ok ? fmaf(1.f - lo[u], sigmoid_f(rf[u]), lo[u]) : 0.f;
-          s_q[i] = ok ? silu_f(rq[u]) : 0.f;
-        }
+        if (i < nt * NP) { s_f[i] = rf[u]; s_q[i] = rq[u]; }
       }
     }
     for (int i = tid; i < nt * PB; i += blockDim.x) {

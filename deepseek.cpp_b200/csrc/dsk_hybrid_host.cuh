@@ -257,6 +257,7 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_mma<HEPI_GEGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_SIGMUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
+  cudaFuncSetAttribute(gemm_mma<HEPI_LINGATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(hgrn2_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(hgrn2_scan<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(hgrn2_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
@@ -1023,6 +1024,7 @@ static void launch_gemm_mma(int epi, const GemmP& P, int Z, int tile_cap, cudaSt
     case HEPI_GEGLU: gemm_mma<HEPI_GEGLU><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_SIGMUL: gemm_mma<HEPI_SIGMUL><<<grid, 256, kMmaSmem, st>>>(P); break;
     case HEPI_RELU2: gemm_mma<HEPI_RELU2><<<grid, 256, kMmaSmem, st>>>(P); break;
+    case HEPI_LINGATE: gemm_mma<HEPI_LINGATE><<<grid, 256, kMmaSmem, st>>>(P); break;
     default: gemm_mma<HEPI_GELU_MUL><<<grid, 256, kMmaSmem, st>>>(P); break;
   }
 }
@@ -1039,6 +1041,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_GEGLU: gemv_rows<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_SIGMUL: gemv_rows<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
       case HEPI_RELU2: gemv_rows<WT, HEPI_RELU2><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_LINGATE: gemv_rows<WT, HEPI_LINGATE><<<grid, 256, 0, st>>>(P); break;
       default: gemv_rows<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   } else {
@@ -1051,6 +1054,7 @@ static void launch_gemm_t(int epi, const GemmP& P, int Z, bool small, int tile_c
       case HEPI_GEGLU: gemm_tiled<WT, HEPI_GEGLU><<<grid, 256, 0, st>>>(P); break;
       case HEPI_SIGMUL: gemm_tiled<WT, HEPI_SIGMUL><<<grid, 256, 0, st>>>(P); break;
       case HEPI_RELU2: gemm_tiled<WT, HEPI_RELU2><<<grid, 256, 0, st>>>(P); break;
+      case HEPI_LINGATE: gemm_tiled<WT, HEPI_LINGATE><<<grid, 256, 0, st>>>(P); break;
       default: gemm_tiled<WT, HEPI_GELU_MUL><<<grid, 256, 0, st>>>(P); break;
     }
   }
@@ -1093,17 +1097,17 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
 #undef DSK_SCAN
 }
 
-static void launch_hgrn2(const dsk_layer_spec& sp, const float* proj, int ld, const float* lower, float* state, float* out, int T, cudaStream_t st) {
+static void launch_hgrn2(const dsk_layer_spec& sp, const float* proj, int ld, float* state, float* out, int T, cudaStream_t st) {
   const int H = sp.lin_heads, N = sp.lin_dim, P = sp.lin_vdim;
   int PB = std::min(P, 64);   // value channels per CTA: fewer when the heads alone would leave most SMs idle
-  while (PB > 8 && H * ((P + PB - 1) / PB) < 148) PB /= 2;
+  while (PB > 16 && H * ((P + PB - 1) / PB) < 148) PB /= 2;
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
   const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
   const int NP = (N + 3) & ~3;
   const size_t smem = (size_t)TB * (2 * NP + PB) * 4;
   const int need = (N + 31) / 32;     // float4 groups of state per thread
-#define DSK_LIN(RQ) hgrn2_scan<RQ><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, lower, state, out, H * P, T, H, N, P, PB, TB)
+#define DSK_LIN(RQ) hgrn2_scan<RQ><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, state, out, H * P, T, H, N, P, PB, TB)
   if (need <= 1) DSK_LIN(1); else if (need <= 2) DSK_LIN(2); else if (need <= 3) DSK_LIN(3); else if (need <= 4) DSK_LIN(4);
   else if (need <= 6) DSK_LIN(6); else DSK_LIN(8);
 #undef DSK_LIN
@@ -1388,11 +1392,11 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     } else if (sp.mixer == DSK_MIX_HGRN2) {
       const int H = sp.lin_heads, HN = H * sp.lin_dim, HP = H * sp.lin_vdim, pw = 2 * HN + HP;
       MK("norm");
-      GemmP In = gp(hin, W, L.lin_in.p, W, S->b0, pw, T, pw, W);   // [raw q | raw forget gate (+ bias) | v]
-      In.bias = L.lin_bias;
-      linear(S, bf, HEPI_STORE, In, 1, st);
+      GemmP In = gp(hin, W, L.lin_in.p, W, S->b0, pw, T, pw, W);   // [silu(q) | forget gate | v]: the activations run in the product's epilogue, in fp32
+      In.bias = L.lin_bias; In.aux = L.lower; In.aux_off = HN;
+      linear(S, bf, HEPI_LINGATE, In, 1, st);
       MK("lin.in");
-      launch_hgrn2(sp, S->b0, pw, L.lower, ls.lin, S->b2, T, st);
+      launch_hgrn2(sp, S->b0, pw, ls.lin, S->b2, T, st);
       MK("lin.scan");
       group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, HP, L.lin_norm, S->b3, HP, HP, H, c.norm_eps, 0, 0.f, nullptr, 0);
       S->launches += 2;

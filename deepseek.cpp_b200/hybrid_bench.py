@@ -2,7 +2,9 @@
 The Desarax sizes run beside the closest DeepSeek model of the framework (true-MLA blocks, fp16) at equal width / depth /
 experts; the Rutulix sizes run beside the closest layer-list model, a Desarax model of latent-attention layers at equal width,
 layer runs, heads, mask size and feed-forward matrix elements; the Sakusun sizes run beside a Rutulix model (the framework's other
-attention-only design with dense feed-forwards) at equal width, depth, heads, window and feed-forward matrix elements.
+attention-only design with dense feed-forwards) at equal width, depth, heads, window and feed-forward matrix elements; the
+Nalizen sizes run beside a Desarax model (the framework's other design with a recurrence, shared attention caches, routed
+feed-forwards and the per-layer token input) at equal width, depth, layer pattern, heads, window and active matrix elements.
 
 Used by `bench.py --hybrid`.  Random weights generated on the GPU (bf16), uploaded through dsk_upload_tensor(src_on_device).
 Decode is the device-side greedy loop (CUDA events around the captured step graph); prefill is dsk_forward_chunk over a prompt
@@ -32,7 +34,134 @@ SIZES = {
                           rel_rows=32, rel_max=1024, lat_dim=64, rot=32, kv_rank=256, q_rank=384, ff=2752, taps=4, buckets=65521),
     "sakusun_large": dict(design="Sakusun", width=2048, vocab=102400, pattern="LALLLALLLALA", att_heads=16, kv_heads=4, att_dim=128, window=1024, keep=4,
                           rel_rows=32, rel_max=2048, lat_dim=128, rot=64, kv_rank=512, q_rank=768, ff=5504, taps=4, buckets=65521),
+    # Nalizen: pattern of recurrent (r) and attention layers (a: own keys and values, A: those of the previous a); the first layer's
+    # feed-forward is dense, the others are routed (experts of two matrices)
+    "nalizen_small": dict(design="Nalizen", width=1024, vocab=32000, pattern="rrarrA", lin_heads=16, lin_dim=64, lin_vdim=64, att_heads=16, kv_heads=4,
+                          att_dim=64, rot=32, window=512, experts=16, top=2, ff=768, side=32),
+    "nalizen_large": dict(design="Nalizen", width=2048, vocab=102400, pattern="rrarrArrarrA", lin_heads=16, lin_dim=128, lin_vdim=128, att_heads=16,
+                          kv_heads=4, att_dim=128, rot=64, window=1024, experts=64, top=6, ff=2112, side=64),
 }
+
+
+def nalizen_config(z):
+    layers, last_a = [], None
+    for i, ch in enumerate(z["pattern"]):
+        # the dense first feed-forward has as many matrix elements as the routed ones have active
+        mlp = {"kind": "dense", "ff": z["top"] * z["ff"] * 2 // 3} if i == 0 else \
+              {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]}}
+        if ch == "r":
+            layers.append({"type": "hgrn2", "mixer": {"heads": z["lin_heads"], "dim": z["lin_dim"], "vdim": z["lin_vdim"]}, "mlp": mlp})
+            continue
+        mx = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
+              "mask": {"size": z["window"]},
+              "rot": {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": z["window"]}}}
+        if ch == "A" and last_a is not None:
+            mx["kv_from"] = last_a
+        else:
+            last_a = i
+        layers.append({"type": "attention", "mixer": mx, "mlp": mlp})
+    return {"architecture": "Nalizen", "vocab": z["vocab"], "width": z["width"], "layers": layers, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+            "token_side": {"dim": z["side"]}}
+
+
+def closest_desarax_of_nalizen(z):
+    """The closest model of the framework to a Nalizen size: Desarax layers in the same pattern (state-space recurrence for the
+    gated linear one with as many heads, value channels and state rows; latent attention with a latent as wide as the key
+    heads; routed GLU experts of three matrices with as many active elements as the two-matrix experts), same width, window,
+    experts and token input."""
+    return dict(width=z["width"], vocab=z["vocab"], pattern=z["pattern"].replace("r", "s"), heads=z["lin_heads"], vdim=z["lin_vdim"], state=z["lin_dim"],
+                groups=max(1, z["lin_heads"] // 8), conv=4, att_heads=z["att_heads"], att_dim=z["att_dim"], att_vdim=z["att_dim"],
+                kv_rank=z["kv_heads"] * z["att_dim"], window=z["window"], experts=z["experts"], top=z["top"], ff=z["ff"] * 2 // 3, side=z["side"])
+
+
+def mint_nalizen(dsk, torch, cfg, quant, chunk, context, device=0):
+    import hashlib
+    hc, specs = dsk.nalizen_from_config(cfg, quant=quant, max_seq_len=context, chunk=chunk)
+    m = dsk.Model(hc, 0, 1, device, layers=specs)
+    dev = torch.device("cuda", device)
+    W, V, L = cfg["width"], cfg["vocab"], len(cfg["layers"])
+    sd = cfg["token_side"]["dim"]
+
+    def up(name, shape, kind="mat"):
+        torch.manual_seed(int(hashlib.md5(name.encode()).hexdigest()[:8], 16))
+        if kind == "mat":
+            t = torch.randn(*shape, device=dev) * (shape[-1] ** -0.5)
+        elif kind == "embed":
+            t = torch.randn(*shape, device=dev)
+        elif kind == "norm":
+            t = 1.0 + 0.1 * torch.randn(*shape, device=dev)
+        elif kind == "unit":
+            t = torch.empty(*shape, device=dev).uniform_(0.0, 0.9)
+        else:
+            t = 0.1 * torch.randn(*shape, device=dev)
+        t = t.to(torch.bfloat16).contiguous()
+        m.upload_device(name, "BF16", shape, t.data_ptr(), t.numel() * 2)
+        torch.cuda.synchronize()
+
+    up("embed", (V, W), "embed"); up("final.norm", (W,), "norm"); up("final.norm.b", (W,), "small"); up("side.embed", (V, sd * L), "embed")
+    for i, lc in enumerate(cfg["layers"]):
+        p, mx, ff = f"l{i}.", lc["mixer"], lc["mlp"]
+        for nm in ("norm1", "norm2"):
+            up(p + nm, (W,), "norm"); up(p + nm + ".b", (W,), "small")
+        up(p + "shift", (W,), "unit")
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        if lc["type"] == "attention":
+            G = mx["kv_heads"]
+            up(p + "mix.q", (H * D, W)); up(p + "mix.g", (H * Vd, W)); up(p + "mix.o", (W, H * Vd))
+            if "kv_from" not in mx:
+                up(p + "mix.k", (G * D, W)); up(p + "mix.v", (G * Vd, W))
+        else:
+            up(p + "mix.q", (H * D, W)); up(p + "mix.f", (H * D, W)); up(p + "mix.f.b", (H * D,), "small"); up(p + "mix.lower", (H * D,), "unit")
+            up(p + "mix.v", (H * Vd, W)); up(p + "mix.norm", (Vd,), "norm"); up(p + "mix.o", (W, H * Vd))
+        if ff["kind"] == "dense":
+            up(p + "mlp.gate", (ff["ff"], W)); up(p + "mlp.up", (ff["ff"], W)); up(p + "mlp.down", (W, ff["ff"]))
+        else:
+            E, fe = ff["router"]["experts"], ff["expert"]["ff"]
+            up(p + "mlp.router", (E, W)); up(p + "mlp.router.b", (E,), "small")
+            for e in range(E):
+                up(f"{p}mlp.e{e}.up", (fe, W)); up(f"{p}mlp.e{e}.down", (W, fe))
+        up(p + "side.gate", (sd, W)); up(p + "side.proj", (W, sd)); up(p + "side.norm", (W,), "norm")
+    m.finalize()
+    return m
+
+
+def nalizen_matrix_elements(cfg, z):
+    """Matrix elements one token multiplies with (projections, gate, feed-forward, token input, head), and the attention's own
+    multiply-adds per token at the mean number of visible keys (half the window)."""
+    W, n, att = cfg["width"], cfg["width"] * cfg["vocab"], 0.0
+    for lc in cfg["layers"]:
+        mx, ff = lc["mixer"], lc["mlp"]
+        H, D, Vd = mx["heads"], mx["dim"], mx["vdim"]
+        if lc["type"] == "attention":
+            n += H * D * W + 2 * H * Vd * W + (0 if "kv_from" in mx else mx["kv_heads"] * (D + Vd) * W)
+            att += H * (D + Vd) * (z["window"] / 2.0)
+        else:
+            n += (2 * H * D + H * Vd) * W + W * H * Vd
+        n += 3 * ff["ff"] * W if ff["kind"] == "dense" else 2 * ff["router"]["top"] * ff["expert"]["ff"] * W + ff["router"]["experts"] * W
+        n += 2 * cfg["token_side"]["dim"] * W
+    return n, att
+
+
+def run_nalizen(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log):
+    """A Nalizen size and the closest model of the framework (Desarax) at equal size."""
+    z = SIZES[name]
+    cfg = nalizen_config(z)
+    t0 = time.time()
+    m = mint_nalizen(dsk, torch, cfg, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    mat, att = nalizen_matrix_elements(cfg, z)
+    res = [measure_layer_list(m, f"Nalizen {name}", z["vocab"], 2.0 * mat, hbm, tfl, prompt_len, gen, chunk, log,
+                              {"layers": len(z["pattern"]), "width": z["width"], "attention_flops_per_token_fp32": 2.0 * att})]
+    m.close()
+    zd = closest_desarax_of_nalizen(z)
+    cfgd = desarax_config(zd)
+    t0 = time.time()
+    m = mint_desarax(dsk, torch, cfgd, "bf16", chunk, prompt_len + gen + 8)
+    log(f"hybrid/{name}/closest Desarax/bf16: minted {m.resident_bytes() / 1e9:.2f} GB in {time.time() - t0:.1f} s")
+    res.append(measure_layer_list(m, f"Desarax layers at {name}", z["vocab"], 2.0 * active_matrix_elements(cfgd), hbm, tfl, prompt_len, gen, chunk, log,
+                                  {"layers": len(cfgd["layers"]), "width": z["width"]}))
+    m.close()
+    return res
 
 
 def sakusun_config(z):
@@ -364,6 +493,9 @@ def run(dsk, torch, repo, bench_module, sizes=("small", "v2lite_like"), prompt_l
             continue
         if z.get("design") == "Sakusun":
             out["results"] += run_sakusun(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log)
+            continue
+        if z.get("design") == "Nalizen":
+            out["results"] += run_nalizen(dsk, torch, name, hbm, tfl, prompt_len, gen, chunk, log)
             continue
         cfg = desarax_config(z)
         for quant in ("bf16",):

@@ -192,3 +192,71 @@ def test_sakusun_oracle_invariants(so):
     v, k = np.random.RandomState(1).randn(6), np.random.RandomState(2).randn(6)
     assert abs(so.rotate(v, rot, 5) @ so.rotate(k, rot, 2) - so.rotate(v, rot, 9) @ so.rotate(k, rot, 6)) < 1e-9
     assert np.array_equal(so.rotate(v, rot, 7)[4:], v[4:])
+
+
+@pytest.fixture(scope="module")
+def no():
+    import nalizen_oracle
+    return nalizen_oracle
+
+
+def test_nalizen_config_to_layer_specs(no):
+    import dsk
+    cfg = no.small_config()
+    hc, specs = dsk.ARCHITECTURES[cfg["architecture"]](cfg, quant="bf16", max_seq_len=77, chunk=16)
+    assert (hc.dim, hc.vocab_size, hc.n_layers, hc.max_seq_len, hc.chunk, hc.side_dim, hc.loop_times) == (44, 61, 5, 77, 16, 5, 0)
+    assert (hc.block, hc.norm_kind, hc.norm_bias, hc.norm_scalar, hc.tie_head, hc.token_shift, hc.canon_taps, hc.res_gate, hc.layer_scale) == \
+        (dsk.BLOCK_POST, dsk.NORM_LAYER, 1, 0, 1, 1, 0, 0, 0)
+    assert abs(hc.embed_scale - 1.5) < 1e-7 and hc.bigram_buckets == 0
+    a, b, c, d, e = specs
+    assert (a.mixer, a.att_heads, a.att_kv_heads, a.att_dim, a.att_vdim, a.att_mask, a.att_window, a.att_kv_from) == (dsk.MIX_GQA, 6, 2, 10, 6, dsk.MASK_WINDOW, 7, -1)
+    assert (a.att_value_proj, a.att_bias, a.att_sink, a.att_talk, a.att_out_gate, a.att_qk_norm, a.rot_layout, a.rot_scale, a.rot_dims, a.rot_original) == \
+        (1, 0, 0, 0, 1, dsk.QKNORM_HEAD, dsk.ROT_HALF, dsk.ROTSCALE_BANDS, 6, 40)
+    assert (a.rot_factor, a.rot_fast, a.rot_slow) == (4.0, 3.0, 1.0) and abs(a.rot_base - 50.0) < 1e-4 and abs(a.att_scale - 0.6) < 1e-6
+    assert (a.ff_kind, a.ff_hidden, a.ff_act) == (dsk.FF_DENSE, 28, dsk.ACT_GEGLU)
+    assert (b.mixer, b.lin_heads, b.lin_dim, b.lin_vdim) == (dsk.MIX_HGRN2, 3, 5, 7)
+    assert (b.ff_kind, b.ff_router, b.ff_expert, b.ff_experts, b.ff_top, b.ff_hidden) == (dsk.FF_MOE, dsk.ROUTER_TOP_SOFTMAX, dsk.EXPERT_RELU2, 5, 2, 12)
+    assert (c.att_kv_from, c.att_window, c.ff_experts, c.ff_top) == (0, 4, 7, 3) and d.ff_kind == dsk.FF_NONE
+    assert (e.rot_factor, e.rot_dims, e.att_kv_heads, e.att_kv_from) == (0.0, 12, 1, -1)
+    m = cfg["layers"][4]["mixer"]
+    del m["rot"], m["mask"], m["kv_heads"]
+    del cfg["token_side"], cfg["embedding"]
+    hc, specs = dsk.nalizen_from_config(cfg)
+    assert (specs[4].rot_dims, specs[4].att_window, specs[4].att_kv_heads, hc.side_dim, hc.embed_scale) == (0, 1 << 30, 2, 0, 1.0)
+    cfg["layers"][1]["type"] = "mamba2"
+    with pytest.raises(dsk.DskError):
+        dsk.nalizen_from_config(cfg)
+
+
+def test_nalizen_oracle_invariants(no):
+    """(1) a sequence fed token by token equals the whole; (2) the rotation depends on the position difference only, pairs the two
+    halves of the rotated part and leaves the entries beyond `dims` alone; (3) the frequency bands; (4) the recurrence with a forget
+    gate of 1 keeps its state and with 0 holds the last value; (5) the token shift; (6) the layer norm."""
+    cfg = no.small_config()
+    W = no.random_weights(cfg, 5)
+    toks = np.arange(20) % 61
+    whole = no.run(cfg, W, toks)[0]
+    seq = no.Sequence(cfg, W)
+    assert np.allclose(np.array([seq.feed(int(t)) for t in toks]), whole, rtol=0, atol=1e-12)
+    rot = {"dims": 4, "base": 50.0}
+    v, k = np.random.RandomState(1).randn(6), np.random.RandomState(2).randn(6)
+    assert abs(no.rotate_half(v, rot, 5) @ no.rotate_half(k, rot, 2) - no.rotate_half(v, rot, 9) @ no.rotate_half(k, rot, 6)) < 1e-9
+    assert np.array_equal(no.rotate_half(v, rot, 7)[4:], v[4:])
+    one = no.rotate_half(np.array([1.0, 0.0, 0.0, 0.0, 9.0]), {"dims": 4, "base": 1.0}, 1)       # entry 0 turns into entry 2, not 1
+    assert np.allclose(one, [np.cos(1.0), 0.0, np.sin(1.0), 0.0, 9.0])
+    sc = {"factor": 10.0, "low": 1.0, "high": 2.0, "original": 100}
+    f = no.rot_frequencies({"dims": 8, "base": 1000.0, "scaling": sc})
+    p = no.rot_frequencies({"dims": 8, "base": 1000.0})
+    assert f[0] == p[0] and abs(f[3] - p[3] / 10.0) < 1e-15                                       # wavelengths 6.3 and 1117 against the bounds 50 and 100
+    mid = 2.0 * np.pi / 75.0
+    s = (100.0 / 75.0 - 1.0) / (2.0 - 1.0)
+    g = no.rot_frequencies({"dims": 2, "base": 1.0, "scaling": sc})                               # base 1: frequency 1, wavelength 6.3: kept
+    assert g == [1.0] and abs(((1 - s) * mid / 10.0 + s * mid) / mid - (0.1 + 0.9 * s)) < 1e-12
+    mx = {"heads": 1, "dim": 2, "vdim": 3}
+    Wl = {"q": np.eye(2, 4), "v": np.eye(3, 4), "f": np.zeros((2, 4)), "f.b": np.zeros(2), "lower": np.array([1.0, 0.0]), "norm": np.ones(3), "o": np.eye(3)}
+    S = np.arange(6.0).reshape(1, 2, 3)
+    no.hgrn2_step({"m." + k: v for k, v in Wl.items()}, "m.", mx, np.array([1.0, 2.0, 3.0, 4.0]), S, 1e-5)
+    assert np.array_equal(S[0, 0], [0.0, 1.0, 2.0]) and np.allclose(S[0, 1], 0.5 * np.array([3.0, 4.0, 5.0]) + 0.5 * np.array([1.0, 2.0, 3.0]))
+    assert np.allclose(no.token_shift(np.array([1.0, 2.0]), np.array([3.0, 6.0]), np.array([0.0, 0.25])), [1.0, 3.0])
+    y = no.layer_norm(np.array([1.0, 3.0]), np.array([2.0, 2.0]), np.array([0.5, 0.5]), 0.0)
+    assert np.allclose(y, [-1.5, 2.5])
