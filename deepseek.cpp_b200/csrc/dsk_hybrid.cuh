@@ -872,14 +872,12 @@ __global__ void shift_carry(const float* __restrict__ x, int ld, float* __restri
 // Inputs of TB tokens at a time are staged in shared memory.
 // ---------------------------------------------------------------------------------------------------------------------
 template <int RQ>
-__global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
+__global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
                                                   float* __restrict__ state, float* __restrict__ out,
                                                   int ld_out, int T, int H, int N, int P, int PB, int TB) {
   extern __shared__ __align__(16) float sm[];
   const int NP = (N + 3) & ~3;      // staged rows are padded to whole float4s
-  float* s_f = sm;                  // [TB][NP]
-  float* s_q = s_f + TB * NP;       // [TB][NP]
-  float* s_v = s_q + TB * NP;       // [TB][PB]
+  const int per = TB * (2 * NP + PB);   // floats of one staging buffer: f [TB][NP], q [TB][NP], v [TB][PB]
   const int h = blockIdx.x, p0 = blockIdx.y * PB;
   const int tid = threadIdx.x, pl = tid >> 3, s = tid & 7, p = p0 + pl;
   const bool pok = pl < PB && p < P;
@@ -891,30 +889,55 @@ __global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj
       const int n = 4 * (s + 8 * j) + k;
       S[j][k] = (pok && n < N) ? state[((size_t)h * N + n) * P + p] : 0.f;
     }
-  for (int t0 = 0; t0 < T; t0 += TB) {
+  // 16-byte asynchronous copies when every staged run starts on a 16-byte boundary; plain loads otherwise
+  const bool vec = (N & 3) == 0 && (ld & 3) == 0 && (q_off & 3) == 0 && (f_off & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
+  const bool vecv = vec && (P & 3) == 0 && (PB & 3) == 0 && (v_off & 3) == 0 && p0 + PB <= P;
+  // Inputs of TB tokens go into one of two buffers while the recurrence runs over the other
+  auto stage = [&](int buf, int t0) {
+    float* s_f = sm + buf * per;
+    float* s_q = s_f + TB * NP;
+    float* s_v = s_q + TB * NP;
     const int nt = min(TB, T - t0);
-    __syncthreads();
-    for (int base = 0; base < nt * NP; base += 4 * (int)blockDim.x) {   // four elements per thread and pass: eight loads in flight
-      float rf[4], rq[4];
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        const int i = base + u * (int)blockDim.x + tid;
+    if (vec) {
+      const int n4 = N >> 2;
+      for (int i = tid; i < nt * n4; i += blockDim.x) {
+        const int tt = i / n4, c = (i - tt * n4) * 4;
+        const float* src = proj + (size_t)(t0 + tt) * ld + h * N + c;
+        cp_async_16(s_f + tt * NP + c, src + f_off, 16);
+        cp_async_16(s_q + tt * NP + c, src + q_off, 16);
+      }
+    } else {
+      for (int i = tid; i < nt * NP; i += blockDim.x) {
         const int tt = i / NP, n = i - tt * NP;
-        const bool ok = i < nt * NP && n < N;      // padding rows: f = 0, q = 0 (they never reach the output or the stored state)
-        rf[u] = ok ? proj[(size_t)(t0 + tt) * ld + f_off + h * N + n] : 0.f;
-        rq[u] = ok ? proj[(size_t)(t0 + tt) * ld + q_off + h * N + n] : 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        const int i = base + u * (int)blockDim.x + tid;
-        if (i < nt * NP) { s_f[i] = rf[u]; s_q[i] = rq[u]; }
+        const bool ok = n < N;       // padding rows: f = 0, q = 0 (they never reach the output or the stored state)
+        s_f[i] = ok ? proj[(size_t)(t0 + tt) * ld + f_off + h * N + n] : 0.f;
+        s_q[i] = ok ? proj[(size_t)(t0 + tt) * ld + q_off + h * N + n] : 0.f;
       }
     }
-    for (int i = tid; i < nt * PB; i += blockDim.x) {
-      const int tt = i / PB, k = i - tt * PB, pp = p0 + k;
-      s_v[i] = pp < P ? proj[(size_t)(t0 + tt) * ld + v_off + h * P + pp] : 0.f;
+    if (vecv) {
+      const int b4 = PB >> 2;
+      for (int i = tid; i < nt * b4; i += blockDim.x) {
+        const int tt = i / b4, c = (i - tt * b4) * 4;
+        cp_async_16(s_v + tt * PB + c, proj + (size_t)(t0 + tt) * ld + v_off + h * P + p0 + c, 16);
+      }
+    } else {
+      for (int i = tid; i < nt * PB; i += blockDim.x) {
+        const int tt = i / PB, k = i - tt * PB, pp = p0 + k;
+        s_v[i] = pp < P ? proj[(size_t)(t0 + tt) * ld + v_off + h * P + pp] : 0.f;
+      }
     }
+    cp_async_commit();
+  };
+  const int nb = (T + TB - 1) / TB;
+  stage(0, 0);
+  for (int b = 0; b < nb; b++) {
+    if (b + 1 < nb) { stage((b + 1) & 1, (b + 1) * TB); cp_async_wait<1>(); }   // the block before the one just issued has landed
+    else cp_async_wait<0>();
     __syncthreads();
+    const float* s_f = sm + (b & 1) * per;
+    const float* s_q = s_f + TB * NP;
+    const float* s_v = s_q + TB * NP;
+    const int t0 = b * TB, nt = min(TB, T - t0);
     for (int tt = 0; tt < nt; tt++) {
       const float xv = pl < PB ? s_v[tt * PB + pl] : 0.f;
       float y0 = 0.f, y1 = 0.f;
@@ -936,6 +959,7 @@ __global__ void __launch_bounds__(512) hgrn2_scan(const float* __restrict__ proj
       y += __shfl_xor_sync(0xffffffffu, y, 4);
       if (s == 0 && pok) out[(size_t)(t0 + tt) * ld_out + h * P + p] = y;
     }
+    __syncthreads();   // the buffer is free for the block after next
   }
 #pragma unroll
   for (int j = 0; j < RQ; j++)
@@ -1170,6 +1194,8 @@ __global__ void __launch_bounds__(128) softmax_band(float* __restrict__ S, int T
 // ---------------------------------------------------------------------------------------------------------------------
 // Layer norm with a weight and an optional bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w (+ b) per row of n values.
 // mode 0: out = result; mode 1: out += alpha * result (a normalised sublayer output added into the residual stream).
+// wgt non-null (rows of up to 256 * kLnRegs values): the row that is normalised is the weighted sum of `top` consecutive input
+// rows, x_t = sum_k wgt[t * top + k] * in[t * top + k] — the outputs of a token's routed experts, combined on the way in.
 // ---------------------------------------------------------------------------------------------------------------------
 // A thread keeps its share of the row in registers (rows of up to 256 * kLnRegs values; longer rows are read again).
 constexpr int kLnRegs = 16;
@@ -1190,15 +1216,22 @@ __device__ __forceinline__ void ln_stats(const float (&v)[kLnRegs], const float*
 }
 
 __global__ void __launch_bounds__(256) layer_norm(const float* __restrict__ in, int ld_in, const float* __restrict__ w, const float* __restrict__ b,
-                                                  float* __restrict__ out, int ld_out, int n, float eps, int mode, float alpha) {
+                                                  float* __restrict__ out, int ld_out, int n, float eps, int mode, float alpha,
+                                                  const float* __restrict__ wgt, int top) {
   __shared__ float red[33];
   const int t = blockIdx.x;
-  const float* x = in + (size_t)t * ld_in;
+  const float* x = in + (size_t)t * (wgt ? top : 1) * ld_in;
   float* o = out + (size_t)t * ld_out;
   float v[kLnRegs];
   const bool cached = n <= 256 * kLnRegs;
 #pragma unroll
-  for (int k = 0; k < kLnRegs; k++) { const int i = threadIdx.x + 256 * k; v[k] = cached && i < n ? x[i] : 0.f; }
+  for (int k = 0; k < kLnRegs; k++) { const int i = threadIdx.x + 256 * k; v[k] = cached && i < n && !wgt ? x[i] : 0.f; }
+  if (wgt)
+    for (int e = 0; e < top; e++) {
+      const float we = wgt[(size_t)t * top + e];
+#pragma unroll
+      for (int k = 0; k < kLnRegs; k++) { const int i = threadIdx.x + 256 * k; if (i < n) v[k] = fmaf(we, x[(size_t)e * ld_in + i], v[k]); }
+    }
   float mean, sc;
   ln_stats(v, x, n, eps, red, mean, sc);
   if (cached) {
@@ -1241,6 +1274,22 @@ __global__ void __launch_bounds__(256) layer_norm_add_norm(const float* __restri
     const int i = threadIdx.x + 256 * k;
     if (i < n) h[t * n + i] = (v[k] - mean) * sc * wh[i];
   }
+}
+
+// RMS norm of every head of a row with one weight vector shared by the heads: out[t][h][:] = in[t][h][:] / rms(in[t][h][:]) * w[:].
+// One warp per (token, head) of P values.
+__global__ void __launch_bounds__(256) head_rmsnorm(const float* __restrict__ in, int ld_in, const float* __restrict__ w, float* __restrict__ out,
+                                                    int ld_out, int T, int H, int P, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long id = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (id >= (long long)T * H) return;
+  const int t = (int)(id / H), h = (int)(id - (long long)t * H);
+  const float* x = in + (size_t)t * ld_in + (size_t)h * P;
+  float* o = out + (size_t)t * ld_out + (size_t)h * P;
+  float ss = 0.f;
+  for (int i = lane; i < P; i += 32) ss = fmaf(x[i], x[i], ss);
+  const float sc = 1.f / sqrtf(warp_sum(ss) / (float)P + eps);
+  for (int i = lane; i < P; i += 32) o[i] = x[i] * sc * w[i];
 }
 
 // x[t][:] += row[:] for the T rows of a step (the per-pass vector of a layer loop)

@@ -80,7 +80,7 @@ struct HLayer {
   // token shift weight; biases of the layer norms; bias of a top-softmax router
   float *shift = nullptr, *norm1_bias = nullptr, *norm2_bias = nullptr, *router_b = nullptr;
   // gated linear recurrence: [q | f | v] rows stacked into one matrix, the forget gate's bias at the f rows of a stacked bias
-  // (zeros elsewhere), lower bounds, and the output norm's weight repeated for every head
+  // (zeros elsewhere), lower bounds, and the output norm's weight (one vector for all heads)
   HTensor lin_in;
   float *lin_bias = nullptr, *lower = nullptr, *lin_norm = nullptr;
   char have_lin[3] = {0, 0, 0}, have_linb = 0;
@@ -523,13 +523,7 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       }
       if (k == "lower") return F32(&L.lower, HN, 0);
       if (k == "o") return MAT(L.o, c.dim, HP);
-      if (k == "norm") {   // one weight vector for all heads: kept repeated per head, so the grouped RMS norm kernel serves
-        if (L.lin_norm) return fail(-4, "tensor %s uploaded twice", name);
-        if (dmalloc(m, (void**)&L.lin_norm, (size_t)HP * 4)) return -2;
-        for (int h = 0; h < s.lin_heads; h++)
-          if (int rc = put(name, dtype, shape, data, nbytes, on_dev, s.lin_vdim, 0, L.lin_norm + (size_t)h * s.lin_vdim, false, 0)) return rc;
-        return 0;
-      }
+      if (k == "norm") return F32(&L.lin_norm, s.lin_vdim, 0);   // one weight vector for all heads
     } else if (s.mixer == DSK_MIX_MLA) {
       const long long H = s.att_heads, DK = s.att_dim + s.att_rot_dim, R = s.att_kv_rank, Q = s.att_q_rank, tot = Q + R + s.att_rot_dim;
       if (k == "dq") return STACK(L.in2, tot, c.dim, 0, Q, &L.have_in2[0]);
@@ -795,7 +789,7 @@ static int launches_per_token(const dsk_model* m) {
     else if (s.mixer == DSK_MIX_GQA) n += (s.att_value_proj ? 5 : 6) + (s.att_out_gate ? 1 : 0);   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, (gate,) o
     else if (s.mixer == DSK_MIX_MLA) n += 10 + (s.att_out_gate ? 1 : 0);   // down-projections, query norm, query up, latent preparation, absorbed query, attention, merge, value up, (gate,) o
     else if (s.mixer != DSK_MIX_MLA && s.mixer != DSK_MIX_HGRN2 && s.mixer != DSK_MIX_GQA) n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
-    if (s.ff_kind == DSK_FF_MOE) n += 5;
+    if (s.ff_kind == DSK_FF_MOE) n += post && M->c.norm_kind == DSK_NORM_LAYER && !M->c.res_gate && M->c.dim <= 256 * kLnRegs ? 4 : 5;
     if (s.ff_kind == DSK_FF_DENSE) n += 2;
     if (M->c.side_dim > 0) n += 3;
   }
@@ -1103,9 +1097,10 @@ static void launch_hgrn2(const dsk_layer_spec& sp, const float* proj, int ld, fl
   while (PB > 16 && H * ((P + PB - 1) / PB) < 148) PB /= 2;
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
   const int threads = ((PB * 8 + 31) / 32) * 32;
-  const int TB = T >= 64 ? 64 : 16;   // tokens staged per round
   const int NP = (N + 3) & ~3;
-  const size_t smem = (size_t)TB * (2 * NP + PB) * 4;
+  int TB = T >= 64 ? 64 : 16;         // tokens staged per round, in two buffers
+  while (TB > 16 && (size_t)2 * TB * (2 * NP + PB) * 4 > 160 * 1024) TB /= 2;
+  const size_t smem = (size_t)2 * TB * (2 * NP + PB) * 4;
   const int need = (N + 31) / 32;     // float4 groups of state per thread
 #define DSK_LIN(RQ) hgrn2_scan<RQ><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, state, out, H * P, T, H, N, P, PB, TB)
   if (need <= 1) DSK_LIN(1); else if (need <= 2) DSK_LIN(2); else if (need <= 3) DSK_LIN(3); else if (need <= 4) DSK_LIN(4);
@@ -1144,7 +1139,7 @@ static void enqueue_head(dsk_model* m, dsk_state* s, int first, int count, cudaS
 
 // the model's norm over the T rows of `in` (width values each): stored into `out`, or added into it times alpha (mode 1)
 static void norm_rows(const dsk_hybrid_config& c, State* S, const float* in, const float* w, const float* b, float* out, int T, int mode, float alpha, cudaStream_t st) {
-  if (c.norm_kind == DSK_NORM_LAYER) layer_norm<<<T, 256, 0, st>>>(in, c.dim, w, b, out, c.dim, c.dim, c.norm_eps, mode, alpha);
+  if (c.norm_kind == DSK_NORM_LAYER) layer_norm<<<T, 256, 0, st>>>(in, c.dim, w, b, out, c.dim, c.dim, c.norm_eps, mode, alpha, nullptr, 0);
   else group_rmsnorm<float><<<T, 256, 0, st>>>(in, c.dim, w, out, c.dim, c.dim, c.norm_groups, c.norm_eps, mode, alpha, nullptr, 0);
   S->launches++;
 }
@@ -1252,6 +1247,8 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       h_ready = true;
     };
     const Sink sink = (sandwich || post) ? to_y : to_x;
+    // a routed feed-forward that closes with a layer norm and no gate: no separate pass for the weighted sum of the experts' outputs
+    const bool combine_in_norm = post && sp.ff_kind == DSK_FF_MOE && c.norm_kind == DSK_NORM_LAYER && !c.res_gate && W <= 256 * kLnRegs;
     if (sp.mixer == DSK_MIX_GQA) {
       const int H = sp.att_heads, G = sp.att_kv_heads, D = sp.att_dim, V = sp.att_vdim, HD = H * D, GD = G * D, GV = G * V, rep = H / G;
       const int keep = sp.att_keep_first;
@@ -1398,7 +1395,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       MK("lin.in");
       launch_hgrn2(sp, S->b0, pw, ls.lin, S->b2, T, st);
       MK("lin.scan");
-      group_rmsnorm<float><<<T, 256, 0, st>>>(S->b2, HP, L.lin_norm, S->b3, HP, HP, H, c.norm_eps, 0, 0.f, nullptr, 0);
+      head_rmsnorm<<<(unsigned)(((long long)T * H + 7) / 8), 256, 0, st>>>(S->b2, HP, L.lin_norm, S->b3, HP, T, H, sp.lin_vdim, c.norm_eps);
       S->launches += 2;
       MK("lin.norm");
       GemmP P = gp(S->b3, HP, L.o.p, HP, sink.C, W, T, W, HP);
@@ -1560,7 +1557,9 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
         linear(S, bf, HEPI_STORE, Dn, 1, st, cap);
         MK("moe.down");
       }
-      moe_combine<<<T, 256, 0, st>>>(sink.C, W, S->b3, S->wgt, top, W, sink.alpha, sink.epi == HEPI_ADD ? 1 : 0);
+      if (combine_in_norm) {   // x += ln(sum_k w_k y_k): the weighted sum of the experts' outputs is taken by the closing layer norm as it reads its row
+        layer_norm<<<T, 256, 0, st>>>(S->b3, W, L.close2, L.norm2_bias, S->x, W, W, c.norm_eps, 1, mult, S->wgt, top);
+      } else moe_combine<<<T, 256, 0, st>>>(sink.C, W, S->b3, S->wgt, top, W, sink.alpha, sink.epi == HEPI_ADD ? 1 : 0);
       S->launches++;
       MK("moe.combine");
     }
@@ -1568,7 +1567,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       close_run(L.norm2b);
       MK("norm");
     }
-    if (post && sp.ff_kind != DSK_FF_NONE) {
+    if (post && sp.ff_kind != DSK_FF_NONE && !combine_in_norm) {
       if (small_post && has_next) { close_open(L.rg2, L.rg2_b, L.close2, M->L[M->runs[ri + 1].layer].canon1, ring_of(ri + 1, 0)); h_ready = true; }
       else close_post(L.rg2, L.rg2_b, L.close2, L.norm2_bias);
       MK("norm");
