@@ -600,6 +600,44 @@ __global__ void __launch_bounds__(128) close_open_small(const float* __restrict_
   }
 }
 
+// Decode-sized steps (T <= kCloseOpenTokens): the end of a layer whose last part is an RMS-normed addition, and the token shift that
+// opens the next layer, in one kernel:   x_t += alpha * rms(y_t) * w;   hs_t = x_t + (x_(t-1) - x_t) * mu   (mu null: no shift follows).
+// `carry` [ch] holds the next layer's input at the token before the step and receives the step's last row.  A CTA owns 128
+// channels over all tokens of the step; every CTA sums the squares of the whole rows of y itself, so no CTA waits for another.
+__global__ void __launch_bounds__(128) rms_add_shift_small(const float* __restrict__ y, const float* __restrict__ w, float alpha, float eps,
+                                                           float* __restrict__ x, int ld, const float* __restrict__ mu, float* __restrict__ carry,
+                                                           float* __restrict__ hs, int T, int ch, const int* __restrict__ ctl) {
+  __shared__ float red[33];
+  float sc[kCloseOpenTokens];
+#pragma unroll
+  for (int t = 0; t < kCloseOpenTokens; t++) {
+    if (t < T) {
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float* yr = y + (size_t)t * ld;
+      int c = threadIdx.x;
+      for (; c + 3 * 128 < ch; c += 4 * 128) {   // four independent loads per round
+        const float v0 = yr[c], v1 = yr[c + 128], v2 = yr[c + 256], v3 = yr[c + 384];
+        s0 = fmaf(v0, v0, s0); s1 = fmaf(v1, v1, s1); s2 = fmaf(v2, v2, s2); s3 = fmaf(v3, v3, s3);
+      }
+      for (; c < ch; c += 128) { const float v = yr[c]; s0 = fmaf(v, v, s0); }
+      sc[t] = 1.f / sqrtf(block_sum((s0 + s1) + (s2 + s3), red) / (float)ch + eps);
+    } else sc[t] = 0.f;
+  }
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= ch) return;
+  const float wc = w[c], m = mu ? mu[c] : 0.f;
+  float prev = mu && ctl[0] > 0 ? carry[c] : 0.f;
+#pragma unroll
+  for (int t = 0; t < kCloseOpenTokens; t++) {
+    if (t < T) {
+      const float cur = fmaf(alpha, y[(size_t)t * ld + c] * sc[t] * wc, x[(size_t)t * ld + c]);
+      x[(size_t)t * ld + c] = cur;
+      if (mu) { hs[(size_t)t * ld + c] = fmaf(prev - cur, m, cur); prev = cur; }
+    }
+  }
+  if (mu) carry[c] = prev;
+}
+
 template <typename WT> struct WVec;
 template <> struct WVec<float> {
   static constexpr int N = 4;

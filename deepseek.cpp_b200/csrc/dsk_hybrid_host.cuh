@@ -780,7 +780,7 @@ static int launches_per_token(const dsk_model* m) {
   for (const Run& R : M->runs) {
     const HLayer& L = M->L[R.layer];
     const dsk_layer_spec& s = L.sp;
-    if (M->c.token_shift) n += 1;
+    if (M->c.token_shift && (&R == &M->runs[0] || !(post && M->c.side_dim > 0 && M->c.canon_taps <= 0))) n += 1;   // later runs: shifted by the previous run's last kernel
     if (post && M->c.canon_taps <= 0) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0));   // gate, closing norm
     else if (post) n += (s.ff_kind != DSK_FF_NONE ? 2 : 1) * (1 + (M->c.res_gate ? 1 : 0)) + (&R == &M->runs[0] && M->c.canon_taps > 0 ? 1 : 0);   // gate, closing norm + next convolution in one
     else if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
@@ -1180,6 +1180,7 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
   // sandwich blocks of layer norms: "x += ln(y); h = ln(x)" runs as one kernel (not while the residual stream is being recorded)
   const bool fuse = fused_norms(c) && !trace;
   bool h_ready = false;   // S->h already holds the norm that opens the coming run (or the final norm)
+  bool hs_ready = false;  // S->hs already holds the token-shifted input of the coming run's mixer
   for (size_t ri = 0; ri < M->runs.size(); ri++) {
     const Run& run = M->runs[ri];
     const int li = run.layer;
@@ -1230,7 +1231,8 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
     }
     h_ready = false;
     const float* hff = hin;   // what a feed-forward of a parallel block reads: the mixer's input ahead of the token shift
-    if (c.token_shift) {      // the mixer reads its input blended with the previous token's; the step's last row is carried on
+    if (c.token_shift && hs_ready) { hin = S->hs; hs_ready = false; }   // the previous run's last kernel shifted already
+    else if (c.token_shift) {      // the mixer reads its input blended with the previous token's; the step's last row is carried on
       const int ty = (T + kCanonTokens - 1) / kCanonTokens;
       token_shift<<<dim3((unsigned)((W + 127) / 128), (unsigned)ty), 128, 0, st>>>(hin, W, L.shift, ls.shift, S->hs, W, T, W, S->d_ctl);
       S->launches++;
@@ -1578,7 +1580,13 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       P.aux = M->side_embed.p; P.aux_row = S->d_tok; P.aux_ld = sd * c.n_layers; P.aux_off = li * sd;
       linear(S, bf, HEPI_GELU_MUL, P, 1, st);
       linear(S, bf, HEPI_STORE, gp(S->b1, sd, L.sproj.p, sd, S->h, W, T, W, sd), 1, st);
-      group_rmsnorm<float><<<T, 256, 0, st>>>(S->h, W, L.snorm, S->x, W, W, 1, c.norm_eps, 1, mult, nullptr, 0);
+      // decode-sized steps of post-norm blocks: the normed addition and the next layer's token shift in one launch over 128-channel CTAs
+      if (post && c.canon_taps <= 0 && T <= kCloseOpenTokens && !trace) {
+        const bool next_shift = c.token_shift && has_next;
+        rms_add_shift_small<<<(W + 127) / 128, 128, 0, st>>>(S->h, L.snorm, mult, c.norm_eps, S->x, W, next_shift ? M->L[M->runs[ri + 1].layer].shift : nullptr,
+                                                             next_shift ? S->L[ri + 1].shift : nullptr, S->hs, T, W, S->d_ctl);
+        hs_ready = next_shift;
+      } else group_rmsnorm<float><<<T, 256, 0, st>>>(S->h, W, L.snorm, S->x, W, W, 1, c.norm_eps, 1, mult, nullptr, 0);
       S->launches++;
       MK("side");
     }
