@@ -1145,7 +1145,8 @@ __global__ void __launch_bounds__(256) latent_swa_attn(const float* __restrict__
 
 // merges the NS partial softmax results of one (token, head): out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s.
 // Grid (token x head, blocks of 128 columns): a thread owns one column and reads its NS partial values with independent loads.
-__global__ void __launch_bounds__(128) latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS) {
+__global__ void __launch_bounds__(128) latent_swa_merge(const float* __restrict__ part, float* __restrict__ out, int R, int NS,
+                                                        const float* __restrict__ gate = nullptr, int ld_gate = 0, int H = 1) {
   __shared__ float wts[64], ms[64];   // NS <= 64 (kAttnSplitMax)
   const size_t th = blockIdx.x;
   const float* pp = part + th * NS * (R + 2);
@@ -1168,7 +1169,16 @@ __global__ void __launch_bounds__(128) latent_swa_merge(const float* __restrict_
     a0 = fmaf(wts[s], v0, a0); a1 = fmaf(wts[s + 1], v1, a1); a2 = fmaf(wts[s + 2], v2, a2); a3 = fmaf(wts[s + 3], v3, a3);
   }
   for (; s < NS; s++) a0 = fmaf(wts[s], pp[(size_t)s * (R + 2) + 2 + r], a0);
-  out[th * R + r] = ((a0 + a1) + (a2 + a3)) * inv;
+  // gate (nullable): row th = token * H + head is multiplied by sigmoid(gate[token][head * R + r])
+  const float gt = gate ? sigmoid_f(gate[(th / H) * (size_t)ld_gate + (th % H) * (size_t)R + r]) : 1.f;
+  out[th * R + r] = ((a0 + a1) + (a2 + a3)) * inv * gt;
+}
+
+// out[t][c] *= sigmoid(gate[t][c]) for the n columns of T rows (an output gate whose raw values came out of a stacked projection)
+__global__ void gate_rows(float* __restrict__ out, int ld_out, const float* __restrict__ gate, int ld_gate, int n) {
+  float* o = out + (size_t)blockIdx.x * ld_out;
+  const float* g = gate + (size_t)blockIdx.x * ld_gate;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) o[c] *= sigmoid_f(g[c]);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1426,7 +1436,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope(const float* __restrict__ q,
 // Keys [ring][G*D] and values [ring][G*Dv] are ring caches (position j in row j % ring).  Tiles of 32 keys are staged in shared
 // memory; warp w owns heads w, w + 8, ... with their running maximum, sum and weighted value sum in shared memory (online
 // softmax, fp32).  NS > 1: the key range is cut into NS shares over blockIdx.y, partial results {m, l, acc[Dv]} go to `part`
-// in the layout latent_swa_merge reads.
+// in the layout latent_swa_merge reads.  Without score mixing the key heads may be dealt over gridDim.z CTAs (G / gridDim.z key
+// heads with their query heads each), which stage only their own slice of the key rows.  gate (nullable, row pitch ld_gate):
+// the output is multiplied by sigmoid(gate[t][h * Dv + r]) (an output gate on the concatenated heads; with NS > 1 the merge does it).
 // ---------------------------------------------------------------------------------------------------------------------
 __host__ __device__ inline size_t gqa_attn_smem_floats(int H, int G, int D, int Dv) {
   return (size_t)H * D + (size_t)H * 32 + (size_t)32 * (G * D + 1) + 2 * (size_t)H + (size_t)H * Dv + (size_t)H * H + 8 * 32 + 32 + 32;
@@ -1434,13 +1446,14 @@ __host__ __device__ inline size_t gqa_attn_smem_floats(int H, int G, int D, int 
 __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
                                                 float* __restrict__ out, const float* __restrict__ talk, int T, int H, int G, int D,
                                                 int Dv, const int* __restrict__ ctl, int mask, int span, int ring, float scale, int NS,
-                                                float* __restrict__ part, ScoreMods mods) {
+                                                float* __restrict__ part, ScoreMods mods, const float* __restrict__ gate, int ld_gate) {
   extern __shared__ float sm[];
   const int GD = G * D, GV = G * Dv, rep = H / G;
-  float* qs = sm;                              // [H][D]
-  float* sc = qs + (size_t)H * D;              // [H][32] raw scores of the tile
-  float* ks = sc + (size_t)H * 32;             // [32][GD + 1]
-  float* ms = ks + (size_t)32 * (GD + 1);      // [H] running maximum
+  const int GL = G / (int)gridDim.z, g0 = (int)blockIdx.z * GL, h0 = g0 * rep, HL = GL * rep, GDl = GL * D;   // this CTA's key heads and query heads
+  float* qs = sm;                              // [HL][D]   (the arrays are sized for all heads; a CTA uses the rows of its own)
+  float* sc = qs + (size_t)H * D;              // [HL][32] raw scores of the tile
+  float* ks = sc + (size_t)H * 32;             // [32][GDl + 1]
+  float* ms = ks + (size_t)32 * (GD + 1);      // [HL] running maximum
   float* ls = ms + H;                          // [H] running sum
   float* accs = ls + H;                        // [H][Dv]
   float* tk = accs + (size_t)H * Dv;           // [H][H]
@@ -1458,9 +1471,9 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
     hi = min(hi, lo + per * 32 - 1);
   }
   auto key_pos = [&](int v) { return v < nk ? v : j_lo + v - nk; };
-  for (int e = tid; e < H * D; e += blockDim.x) qs[e] = q[(size_t)t * H * D + e];
-  for (int e = tid; e < H; e += blockDim.x) { ms[e] = -1e30f; ls[e] = 0.f; }
-  for (int e = tid; e < H * Dv; e += blockDim.x) accs[e] = 0.f;
+  for (int e = tid; e < HL * D; e += blockDim.x) qs[e] = q[((size_t)t * H + h0) * D + e];
+  for (int e = tid; e < HL; e += blockDim.x) { ms[e] = -1e30f; ls[e] = 0.f; }
+  for (int e = tid; e < HL * Dv; e += blockDim.x) accs[e] = 0.f;
   if (talk) for (int e = tid; e < H * H; e += blockDim.x) tk[e] = talk[e];
   for (int j0 = lo; j0 <= hi; j0 += 32) {
     __syncthreads();
@@ -1469,24 +1482,25 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
       rowoff[tid] = (int)cache_row(p, keep, ring);
       kdist[tid] = i - p;
     }
-    if ((GD & 3) == 0) {   // 16-byte loads, several in flight per thread (the rows are 16-byte aligned: GD * 4 bytes each)
-      const int GD4 = GD >> 2;
+    if ((GD & 3) == 0 && ((D & 3) == 0 || gridDim.z == 1)) {   // 16-byte loads, several in flight per thread (rows and head slices start on 16-byte boundaries)
+      const int GD4 = GDl >> 2;
 #pragma unroll 8
       for (int e = tid; e < 32 * GD4; e += 256) {
         const int jj = e / GD4, r = (e - jj * GD4) * 4, j = j0 + jj;
-        const float4 v = j <= hi ? *reinterpret_cast<const float4*>(kc + (size_t)cache_row(key_pos(j), keep, ring) * GD + r) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float* d = ks + jj * (GD + 1) + r;
+        const float4 v = j <= hi ? *reinterpret_cast<const float4*>(kc + (size_t)cache_row(key_pos(j), keep, ring) * GD + g0 * D + r) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float* d = ks + jj * (GDl + 1) + r;
         d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
       }
     } else {
-      for (int e = tid; e < 32 * GD; e += blockDim.x) {
-        const int jj = e / GD, r = e - jj * GD, j = j0 + jj;
-        ks[jj * (GD + 1) + r] = j <= hi ? kc[(size_t)cache_row(key_pos(j), keep, ring) * GD + r] : 0.f;
+      for (int e = tid; e < 32 * GDl; e += blockDim.x) {
+        const int jj = e / GDl, r = e - jj * GDl, j = j0 + jj;
+        ks[jj * (GDl + 1) + r] = j <= hi ? kc[(size_t)cache_row(key_pos(j), keep, ring) * GD + g0 * D + r] : 0.f;
       }
     }
     __syncthreads();
-    for (int h = w; h < H; h += 8) {   // raw scores: lane = key
-      const float* kr = ks + lane * (GD + 1) + (h / rep) * D;
+    for (int hl = w; hl < HL; hl += 8) {   // raw scores: lane = key
+      const int h = hl;                  // row of the CTA's own arrays
+      const float* kr = ks + lane * (GDl + 1) + (hl / rep) * D;
       const float* qr = qs + h * D;
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       int d = 0;
@@ -1499,13 +1513,13 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
     }
     __syncthreads();
     const bool valid = j0 + lane <= hi;
-    for (int h = w; h < H; h += 8) {
+    for (int h = w; h < HL; h += 8) {    // h: row of the CTA's own arrays; the head is h0 + h (mixing runs with all heads in one CTA: h0 = 0)
       float s;
       if (talk) {
         s = 0.f;
         for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * 32 + lane], s);
       } else s = sc[h * 32 + lane];
-      s = valid ? mod_score(mods, s, kdist[lane], h, H) : -1e30f;
+      s = valid ? mod_score(mods, s, kdist[lane], h0 + h, H) : -1e30f;
       const float m_old = ms[h];
       const float m_new = fmaxf(m_old, warp_max(s));
       const float corr = expf(m_old - m_new);
@@ -1515,7 +1529,7 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
       __syncwarp();
       // weighted values: lane owns columns lane, lane + 32, ... (four at a time); eight keys per batch, so 32 loads are in flight
       // per lane.  Keys past the tile's end have weight 0 and a row inside the ring (initialised memory), so no branch is needed.
-      const float* vb = vc + (size_t)(h / rep) * Dv;
+      const float* vb = vc + (size_t)((h0 + h) / rep) * Dv;
       const float* pw = ps + w * 32;
       for (int r0 = 0; r0 < Dv; r0 += 128) {
         float a[4];
@@ -1545,21 +1559,25 @@ __global__ void __launch_bounds__(256) gqa_attn(const float* __restrict__ q, con
     }
   }
   __syncthreads();
-  for (int h = w; h < H; h += 8) {
+  for (int h = w; h < HL; h += 8) {
+    const int hg = h0 + h;                // the head
     float m = ms[h], l = ls[h], corr = 1.f;
     if (mods.sink && blockIdx.y == 0) {   // the sink joins the first share like a key with a zero value vector
-      const float sk = mods.sink[h], m_new = fmaxf(m, sk);
+      const float sk = mods.sink[hg], m_new = fmaxf(m, sk);
       corr = expf(m - m_new);
       l = l * corr + expf(sk - m_new);
       m = m_new;
     }
     if (NS > 1) {
-      float* pp = part + (((size_t)t * H + h) * NS + blockIdx.y) * (Dv + 2);
+      float* pp = part + (((size_t)t * H + hg) * NS + blockIdx.y) * (Dv + 2);
       if (lane == 0) { pp[0] = m; pp[1] = l; }
       for (int r = lane; r < Dv; r += 32) pp[2 + r] = accs[h * Dv + r] * corr;
     } else {
       const float inv = corr / l;
-      for (int r = lane; r < Dv; r += 32) out[((size_t)t * H + h) * Dv + r] = accs[h * Dv + r] * inv;
+      for (int r = lane; r < Dv; r += 32) {
+        const float gt = gate ? sigmoid_f(gate[(size_t)t * ld_gate + (size_t)hg * Dv + r]) : 1.f;
+        out[((size_t)t * H + hg) * Dv + r] = accs[h * Dv + r] * inv * gt;
+      }
     }
   }
 }

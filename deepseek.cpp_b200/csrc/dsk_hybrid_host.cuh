@@ -50,13 +50,14 @@ struct HLayer {
   HTensor kproj;
   float *q_norm = nullptr, *k_norm = nullptr, *talk = nullptr, *rot_freq = nullptr;
   float rot_mag = 1.f;
-  // grouped-query attention with a value matrix: q, k and v rows stacked into one matrix (one product per step) with their biases
+  // grouped-query attention with a value matrix: q, k and v rows (and the output gate's rows, when there is one) stacked into one
+  // matrix (one product per step) with their biases; a layer that reads another layer's keys and values stacks [q | gate]
   HTensor qkv;
   float *qkv_b = nullptr, *rel = nullptr, *sink = nullptr;
   int* rel_bucket = nullptr;        // distance (0 .. att_rel_max) -> row of rel
   int rel_rows = 0;
   float vmix = 0.f;                 // value-mixing weight (mix.vmix), read once at upload
-  char have_qkv[3] = {0, 0, 0}, have_qkvb[3] = {0, 0, 0}, have_vmix = 0;
+  char have_qkv[4] = {0, 0, 0, 0}, have_qkvb[3] = {0, 0, 0}, have_vmix = 0;   // have_qkv[3]: the output gate's rows behind q / k / v
   // latent attention with a rotated key part: the two down-projections stacked [q_rank | kv_rank + rot_dim], query up-projection, output gate
   HTensor in2, uq, gmat;
   float* dq_norm = nullptr;
@@ -203,6 +204,7 @@ static int validate(const dsk_hybrid_config& c, const dsk_layer_spec* L) {
         return fail(-1, "layer %d: unknown rotation layout, rotation scaling or query / key norm", i);
       if (s.rot_scale == DSK_ROTSCALE_BANDS && s.rot_factor > 0.f && (!(s.rot_fast > s.rot_slow) || s.rot_original <= 0))
         return fail(-1, "layer %d: wavelength-band rotation scaling needs high > low and a positive original length", i);
+      if (s.att_out_gate && !s.att_value_proj) return fail(-1, "layer %d: the output gate's rows ride in the stacked q / k / v projection (att_value_proj)", i);
       if (s.att_kv_from >= 0) {
         const int j = s.att_kv_from;
         if (j >= i || L[j].mixer != DSK_MIX_GQA || L[j].att_kv_from >= 0)
@@ -537,15 +539,18 @@ static int upload(dsk_model* m, const char* name, int dtype, const int64_t shape
       if (k == "o") return MAT(L.o, c.dim, H * s.att_vdim);
     } else if (s.mixer == DSK_MIX_GQA) {
       const long long HD = (long long)s.att_heads * s.att_dim, GD = (long long)s.att_kv_heads * s.att_dim, GV = (long long)s.att_kv_heads * s.att_vdim;
-      if (k == "g" && s.att_out_gate) return MAT(L.gmat, (long long)s.att_heads * s.att_vdim, c.dim);
-      if (s.att_kv_from >= 0) {   // reads another layer's keys and values: only the query projection of its own
-        if (k == "q") return MAT(L.q, HD, c.dim);
+      const long long HV = s.att_out_gate ? (long long)s.att_heads * s.att_vdim : 0;
+      if (s.att_kv_from >= 0) {   // reads another layer's keys and values: only the query projection (and gate) of its own
+        if (k == "q") return STACK(L.qkv, HD + HV, c.dim, 0, HD, &L.have_qkv[0]);
+        if (k == "g" && s.att_out_gate) return STACK(L.qkv, HD + HV, c.dim, HD, HV, &L.have_qkv[3]);
       } else if (s.att_value_proj) {
-        const long long tot = HD + GD + GV;
+        const long long tot = HD + GD + GV + HV;
+        if (k == "g" && s.att_out_gate) return STACK(L.qkv, tot, c.dim, HD + GD + GV, HV, &L.have_qkv[3]);
         if (k == "q") return STACK(L.qkv, tot, c.dim, 0, HD, &L.have_qkv[0]);
         if (k == "k") return STACK(L.qkv, tot, c.dim, HD, GD, &L.have_qkv[1]);
         if (k == "v") return STACK(L.qkv, tot, c.dim, HD + GD, GV, &L.have_qkv[2]);
         if (s.att_bias) {
+          if (!L.qkv_b && HV > 0) { if (dmalloc(m, (void**)&L.qkv_b, (size_t)tot * 4)) return -2; CK(cudaMemset(L.qkv_b, 0, (size_t)tot * 4)); }   // no bias on the gate's rows
           if (k == "q.b") return STACKV(&L.qkv_b, tot, 0, HD, &L.have_qkvb[0]);
           if (k == "k.b") return STACKV(&L.qkv_b, tot, HD, GD, &L.have_qkvb[1]);
           if (k == "v.b") return STACKV(&L.qkv_b, tot, HD + GD, GV, &L.have_qkvb[2]);
@@ -678,9 +683,10 @@ static int finalize(dsk_model* m) {
       if (!L.lin_in.present || !L.have_linb || !L.lower || !L.lin_norm || !L.o.present)
         return fail(-5, "layer %d: missing linear-recurrence tensors (mix.q, f, f.b, lower, v, norm, o)", i);
     } else if (s.mixer == DSK_MIX_GQA) {
-      if (s.att_out_gate && !L.gmat.present) return fail(-5, "layer %d: missing tensor mix.g", i);
+      if (s.att_out_gate && !L.have_qkv[3]) return fail(-5, "layer %d: missing tensor mix.g", i);
       if (s.att_kv_from >= 0) {
-        if (!L.q.present) return fail(-5, "layer %d: missing tensor mix.q", i);
+        L.qkv.present = L.have_qkv[0];
+        if (!L.qkv.present) return fail(-5, "layer %d: missing tensor mix.q", i);
       } else if (s.att_value_proj) {
         L.qkv.present = L.have_qkv[0] && L.have_qkv[1] && L.have_qkv[2];
         if (!L.qkv.present || (s.att_bias && !(L.have_qkvb[0] && L.have_qkvb[1] && L.have_qkvb[2]))) return fail(-5, "layer %d: missing attention projections (mix.q, k, v and their biases)", i);
@@ -786,7 +792,7 @@ static int launches_per_token(const dsk_model* m) {
     else if (fused_norms(M->c)) n += 1 + (s.ff_kind != DSK_FF_NONE ? 1 : 0) + (&R == &M->runs[0] ? 1 + (R.pass >= 0 ? 1 : 0) : 0);
     else n += 1 + (R.pass >= 0 ? 1 : 0) + (sandwich ? 1 + (s.ff_kind != DSK_FF_NONE ? 2 : 0) : 0);
     if (s.mixer == DSK_MIX_HGRN2) n += 4;   // stacked projection, recurrence, head norm, o
-    else if (s.mixer == DSK_MIX_GQA) n += (s.att_value_proj ? 5 : 6) + (s.att_out_gate ? 1 : 0);   // q, k (or one stacked q / k / v product), norm + rotation, attention, merge, (gate,) o
+    else if (s.mixer == DSK_MIX_GQA) n += s.att_value_proj ? 5 : 6;   // q, k (or one stacked q / k / v (/ gate) product), norm + rotation, attention, merge, o
     else if (s.mixer == DSK_MIX_MLA) n += 10 + (s.att_out_gate ? 1 : 0);   // down-projections, query norm, query up, latent preparation, absorbed query, attention, merge, value up, (gate,) o
     else if (s.mixer != DSK_MIX_MLA && s.mixer != DSK_MIX_HGRN2 && s.mixer != DSK_MIX_GQA) n += is_ssd(s) ? 5 + (s.ssm_conv > 1 ? 1 : 0) : 5 + (s.att_kv_from < 0 ? 2 : 0);
     if (s.ff_kind == DSK_FF_MOE) n += post && M->c.norm_kind == DSK_NORM_LAYER && !M->c.res_gate && M->c.dim <= 256 * kLnRegs ? 4 : 5;
@@ -875,7 +881,7 @@ static dsk_state* state_create(dsk_model* m) {
         ls.vcache_bytes = rows * GV * 4;
         if (salloc(S, &ls.cache, ls.cache_bytes) || salloc(S, &ls.vcache, ls.vcache_bytes)) return nullptr;
       }
-      mx0 = std::max<size_t>(mx0, sp.att_value_proj ? HD + GD + GV : HD); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
+      mx0 = std::max<size_t>(mx0, (sp.att_value_proj ? HD + GD + GV : HD) + (sp.att_out_gate ? (size_t)sp.att_heads * sp.att_vdim : 0)); mx1 = std::max<size_t>(mx1, GD); mx2 = std::max<size_t>(mx2, HD);
       mx3 = std::max<size_t>(mx3, (size_t)sp.att_heads * sp.att_vdim);
       any_talk |= sp.att_talk != 0;
       if (sp.att_vmix) mxGV = std::max(mxGV, GV);
@@ -1259,13 +1265,16 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
       float *kc = (float*)S->L[R0(M, ri)].cache, *vc = (float*)S->L[R0(M, ri)].vcache;
       const ScoreMods sm{sp.att_softcap, sp.att_rel_max > 0 ? L.rel : nullptr, L.rel_bucket, sp.att_rel_max, sp.att_sink ? L.sink : nullptr, keep};
       MK("norm");
+      const int HV = sp.att_out_gate ? H * V : 0;   // the output gate's raw values come out of the stacked product, behind q / k / v
+      const int ldp = reads ? HD + HV : HD + GD + GV + HV;
+      const float* gate = HV ? S->b0 + (ldp - HV) : nullptr;
       if (reads) {
-        linear(S, bf, HEPI_STORE, gp(hin, W, L.q.p, W, S->b0, HD, T, HD, W), 1, st);
+        linear(S, bf, HEPI_STORE, gp(hin, W, L.qkv.p, W, S->b0, ldp, T, ldp, W), 1, st);
         MK("att.qk");
-        qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, nullptr, nullptr, GD, GV, HD, 0, 0, L.q_norm, nullptr, c.norm_eps, D, sp.rot_dims, L.rot_freq,
+        qk_norm_rope<<<T, 256, 0, st>>>(S->b0, S->b2, HD, nullptr, nullptr, GD, GV, ldp, 0, 0, L.q_norm, nullptr, c.norm_eps, D, sp.rot_dims, L.rot_freq,
                                         L.rot_mag, S->d_ctl, nullptr, nullptr, ring, keep, nullptr, 0.f, nullptr, sp.rot_layout, sp.att_qk_norm);
       } else if (sp.att_value_proj) {   // one product for the stacked q / k / v rows; the first value-mixing layer keeps its values for the later ones
-        const int ld = HD + GD + GV;
+        const int ld = ldp;
         GemmP P = gp(hin, W, L.qkv.p, W, S->b0, ld, T, ld, W);
         P.bias = sp.att_bias ? L.qkv_b : nullptr;
         linear(S, bf, HEPI_STORE, P, 1, st);
@@ -1310,16 +1319,21 @@ static int enqueue_chunk(dsk_model* m, dsk_state* s, int T, int n_want, float* t
           linear(S, false, HEPI_STORE, Ov, H, st);
           MK("att.pv");
         }
+        if (gate) { gate_rows<<<T, 256, 0, st>>>(S->b3, H * V, gate, ldp, H * V); S->launches++; }   // heads *= sigmoid(g h)
       } else {
         int NS = 1;
         if (T <= kAttnSplitTokens) NS = std::max(1, std::min((std::min(sp.att_window, ring) + keep + 31) / 32, kAttnSplitMax));
-        gqa_attn<<<dim3((unsigned)T, (unsigned)NS), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
-            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, ring, sp.att_scale, NS, S->part, sm);
-        if (NS > 1) latent_swa_merge<<<dim3((unsigned)(T * H), (unsigned)((V + 127) / 128)), 128, 0, st>>>(S->part, S->b3, V, NS);
+        // without score mixing the key heads are dealt over CTAs, as few per CTA as keep four query heads (half the warps) busy
+        int GL = G;
+        if (!sp.att_talk)
+          for (int d = G; d >= 1; d--) if (G % d == 0 && d * rep >= 4) GL = d;
+        gqa_attn<<<dim3((unsigned)T, (unsigned)NS, (unsigned)(G / GL)), 256, gqa_attn_smem_floats(H, G, D, V) * 4, st>>>(
+            S->b2, kc, vc, S->b3, sp.att_talk ? L.talk : nullptr, T, H, G, D, V, S->d_ctl, sp.att_mask, sp.att_window, ring, sp.att_scale, NS, S->part, sm,
+            NS > 1 ? nullptr : gate, ldp);
+        if (NS > 1) latent_swa_merge<<<dim3((unsigned)(T * H), (unsigned)((V + 127) / 128)), 128, 0, st>>>(S->part, S->b3, V, NS, gate, ldp, H);
         S->launches += NS > 1 ? 2 : 1;
         MK("att.decode");
       }
-      if (sp.att_out_gate) linear(S, bf, HEPI_SIGMUL, gp(hin, W, L.gmat.p, W, S->b3, H * V, T, H * V, W), 1, st);   // heads *= sigmoid(g h)
       GemmP P = gp(S->b3, H * V, L.o.p, H * V, sink.C, W, T, W, H * V);
       P.alpha = sink.alpha;
       linear(S, bf, sink.epi, P, 1, st);
