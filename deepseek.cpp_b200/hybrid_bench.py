@@ -54,7 +54,7 @@ def nalizen_config(z):
             continue
         mx = {"heads": z["att_heads"], "kv_heads": z["kv_heads"], "dim": z["att_dim"], "vdim": z["att_dim"], "scale": z["att_dim"] ** -0.5,
               "mask": {"size": z["window"]},
-              "rot": {"dims": z["rot"], "base": 10000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": z["window"]}}}
+              "rot": {"dims": z["rot"], "base": 500000.0, "scaling": {"factor": 32.0, "low": 1.0, "high": 8.0, "original": z["window"]}}}
         if ch == "A" and last_a is not None:
             mx["kv_from"] = last_a
         else:
