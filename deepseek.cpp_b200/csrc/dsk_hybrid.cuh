@@ -905,11 +905,12 @@ __global__ void shift_carry(const float* __restrict__ x, int ld, float* __restri
 // Gated linear recurrence (HGRN2 form) over a chunk, one CTA per (head, slice of PB value channels), sequential over the tokens:
 //   S[n][p] <- f[n] S[n][p] + (1 - f[n]) v[p]   (computed as v + f (S - v));   o[p] = sum_n q[n] S[n][p]
 // proj rows hold [q | f | v] at the given offsets (H * N, H * N, H * P wide) with the activations already applied by the
-// projection's epilogue: q = silu(.), f = l + (1 - l) sigmoid(.) in fp32.  state [H][N][P] fp32.  Thread (pl, s) owns value channel
-// p = p0 + pl and 4 RQ rows n = 4 (s + 8 j) + k of S[:, p] in registers; the eight threads of a channel reduce o with shuffles.
-// Inputs of TB tokens at a time are staged in shared memory.
+// projection's epilogue: q = silu(.), f = l + (1 - l) sigmoid(.) in fp32.  state [H][N][P] fp32.  TPC (8, 16 or 32) threads share a
+// value channel: thread (pl, s) owns channel p = p0 + pl and 4 RQ rows n = 4 (s + TPC j) + k of S[:, p] in registers, and the TPC
+// threads of a channel reduce o with shuffles.  More threads per channel mean shorter per-token work per thread and more warps to
+// hide its latencies (the host picks TPC so that the warps fill the SMs).  Inputs of TB tokens at a time are staged in shared memory.
 // ---------------------------------------------------------------------------------------------------------------------
-template <int RQ>
+template <int RQ, int TPC>
 __global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ proj, int ld, int q_off, int f_off, int v_off,
                                                   float* __restrict__ state, float* __restrict__ out,
                                                   int ld_out, int T, int H, int N, int P, int PB, int TB) {
@@ -917,14 +918,14 @@ __global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ p
   const int NP = (N + 3) & ~3;      // staged rows are padded to whole float4s
   const int per = TB * (2 * NP + PB);   // floats of one staging buffer: f [TB][NP], q [TB][NP], v [TB][PB]
   const int h = blockIdx.x, p0 = blockIdx.y * PB;
-  const int tid = threadIdx.x, pl = tid >> 3, s = tid & 7, p = p0 + pl;
+  const int tid = threadIdx.x, pl = tid / TPC, s = tid & (TPC - 1), p = p0 + pl;
   const bool pok = pl < PB && p < P;
   float S[RQ][4];
 #pragma unroll
   for (int j = 0; j < RQ; j++)
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const int n = 4 * (s + 8 * j) + k;
+      const int n = 4 * (s + TPC * j) + k;
       S[j][k] = (pok && n < N) ? state[((size_t)h * N + n) * P + p] : 0.f;
     }
   // 16-byte asynchronous copies when every staged run starts on a 16-byte boundary; plain loads otherwise
@@ -976,12 +977,13 @@ __global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ p
     const float* s_q = s_f + TB * NP;
     const float* s_v = s_q + TB * NP;
     const int t0 = b * TB, nt = min(TB, T - t0);
-    for (int tt = 0; tt < nt; tt++) {
+#pragma unroll 4
+    for (int tt = 0; tt < nt; tt++) {   // unrolled: the loads, the reduction and the shuffles of neighbouring tokens overlap; only S is a chain
       const float xv = pl < PB ? s_v[tt * PB + pl] : 0.f;
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int j = 0; j < RQ; j++) {
-        const int n4 = 4 * (s + 8 * j);
+        const int n4 = 4 * (s + TPC * j);
         if (n4 < NP) {
           const float4 f = *reinterpret_cast<const float4*>(s_f + tt * NP + n4);
           const float4 c = *reinterpret_cast<const float4*>(s_q + tt * NP + n4);
@@ -992,9 +994,8 @@ __global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ p
         }
       }
       float y = y0 + y1;
-      y += __shfl_xor_sync(0xffffffffu, y, 1);
-      y += __shfl_xor_sync(0xffffffffu, y, 2);
-      y += __shfl_xor_sync(0xffffffffu, y, 4);
+#pragma unroll
+      for (int o = 1; o < TPC; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
       if (s == 0 && pok) out[(size_t)(t0 + tt) * ld_out + h * P + p] = y;
     }
     __syncthreads();   // the buffer is free for the block after next
@@ -1003,7 +1004,7 @@ __global__ void __launch_bounds__(512, 1) hgrn2_scan(const float* __restrict__ p
   for (int j = 0; j < RQ; j++)
 #pragma unroll
     for (int k = 0; k < 4; k++) {
-      const int n = 4 * (s + 8 * j) + k;
+      const int n = 4 * (s + TPC * j) + k;
       if (pok && n < N) state[((size_t)h * N + n) * P + p] = S[j][k];
     }
 }

@@ -260,9 +260,12 @@ static void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_mma<HEPI_SIGMUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_RELU2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
   cudaFuncSetAttribute(gemm_mma<HEPI_LINGATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmem);
-  cudaFuncSetAttribute(hgrn2_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(hgrn2_scan<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-  cudaFuncSetAttribute(hgrn2_scan<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<3, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<6, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<3, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+  cudaFuncSetAttribute(hgrn2_scan<1, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big); cudaFuncSetAttribute(hgrn2_scan<2, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(gqa_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   cudaFuncSetAttribute(mix_heads, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
   done = true;
@@ -1099,18 +1102,26 @@ static void launch_scan(const dsk_layer_spec& sp, const float* proj, int ld_proj
 
 static void launch_hgrn2(const dsk_layer_spec& sp, const float* proj, int ld, float* state, float* out, int T, cudaStream_t st) {
   const int H = sp.lin_heads, N = sp.lin_dim, P = sp.lin_vdim;
-  int PB = std::min(P, 64);   // value channels per CTA: fewer when the heads alone would leave most SMs idle
+  // threads per value channel (measured at 16 heads x 128 x 128 and x 64 x 64: 16 threads and 16 channels per CTA are the best split; fewer
+  // channels per CTA repeat the staging of a head's gates and queries in more CTAs, more leave SMs idle)
+  int TPC = N >= 256 ? 32 : N >= 64 ? 16 : 8;
+  if (const char* e = getenv("DSK_LIN_TPC")) { const int v = atoi(e); if ((v == 8 || v == 16 || v == 32) && N >= 4 * v) TPC = v; }   // A/B switch
+  int PB = std::min(P, 512 / TPC);   // value channels per CTA
   while (PB > 16 && H * ((P + PB - 1) / PB) < 148) PB /= 2;
+  if (PB == 16 && H * ((P + 15) / 16) < 74) PB = 8;
+  if (const char* e = getenv("DSK_LIN_PB")) PB = std::max(1, std::min(std::min(P, 512 / TPC), atoi(e)));   // A/B switch
   const dim3 grid((unsigned)H, (unsigned)((P + PB - 1) / PB));
-  const int threads = ((PB * 8 + 31) / 32) * 32;
+  const int threads = ((PB * TPC + 31) / 32) * 32;
   const int NP = (N + 3) & ~3;
   int TB = T >= 64 ? 64 : 16;         // tokens staged per round, in two buffers
   while (TB > 16 && (size_t)2 * TB * (2 * NP + PB) * 4 > 160 * 1024) TB /= 2;
   const size_t smem = (size_t)2 * TB * (2 * NP + PB) * 4;
-  const int need = (N + 31) / 32;     // float4 groups of state per thread
-#define DSK_LIN(RQ) hgrn2_scan<RQ><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, state, out, H * P, T, H, N, P, PB, TB)
-  if (need <= 1) DSK_LIN(1); else if (need <= 2) DSK_LIN(2); else if (need <= 3) DSK_LIN(3); else if (need <= 4) DSK_LIN(4);
-  else if (need <= 6) DSK_LIN(6); else DSK_LIN(8);
+  const int need = (N + 4 * TPC - 1) / (4 * TPC);     // float4 groups of state per thread
+#define DSK_LIN(RQ, C) hgrn2_scan<RQ, C><<<grid, threads, smem, st>>>(proj, ld, 0, H * N, 2 * H * N, state, out, H * P, T, H, N, P, PB, TB)
+  if (TPC == 32) { if (need <= 1) DSK_LIN(1, 32); else DSK_LIN(2, 32); }
+  else if (TPC == 16) { if (need <= 1) DSK_LIN(1, 16); else if (need <= 2) DSK_LIN(2, 16); else if (need <= 3) DSK_LIN(3, 16); else DSK_LIN(4, 16); }
+  else if (need <= 1) DSK_LIN(1, 8); else if (need <= 2) DSK_LIN(2, 8); else if (need <= 3) DSK_LIN(3, 8); else if (need <= 4) DSK_LIN(4, 8);
+  else if (need <= 6) DSK_LIN(6, 8); else DSK_LIN(8, 8);
 #undef DSK_LIN
 }
 
