@@ -21,6 +21,8 @@
 //                     and optional mixing of the heads' scores before the softmax (decode-sized steps)
 //   pack_ring_kv, mix_heads, softmax_band   the same attention for portions, between three matrix products
 //   token_shift       h_t + (h_(t-1) - h_t) * mu in front of a mixer, the last row carried from step to step
+//   rms_add_shift_small   decode-sized steps: an RMS-normed addition into the stream and the next layer's token shift in one launch
+//   head_rmsnorm      RMS norm per head with one weight vector for all heads
 //   hgrn2_scan        the gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T silu(q), f = l + (1 - l) sigmoid(.)
 //   moe_route         sigmoid scores, selection by score + correction, weights = normalised scores x scale; or the largest
 //                     logits with a softmax over the chosen ones
