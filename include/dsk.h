@@ -131,8 +131,9 @@ typedef struct dsk_layer_spec {
   int ssm_heads, ssm_vdim, ssm_state, ssm_groups, ssm_conv, ssm_norm_groups;   /* DSK_MIX_SSD */
   int att_heads, att_dim, att_vdim, att_kv_rank, att_window, att_kv_from;      /* DSK_MIX_LATENT_SWA; att_kv_from < 0: own latent */
   float att_scale;
-  int ff_kind, ff_experts, ff_top, ff_hidden;                           /* DSK_FF_MOE: sigmoid router with selection bias, */
-  float ff_limit, ff_router_scale;                                      /* clamped GLU experts g*sigmoid(1.702 g)*(u + 1)   */
+  int ff_kind, ff_experts, ff_top, ff_hidden;                           /* DSK_FF_MOE: sigmoid router with selection bias,   */
+  float ff_limit, ff_router_scale;                                      /* clamped GLU experts g*sigmoid(1.702 g)*(u + 1),   */
+                                                                        /* unless ff_router / ff_expert (below) say otherwise */
   int att_mask;                                                         /* DSK_MASK_* of both attention mixers */
   int att_kv_heads, att_talk;                                           /* DSK_MIX_GQA (with att_heads, att_dim, att_vdim, att_scale, att_window) */
   int rot_dims, rot_original;                                           /* rot_dims 0: no rotation */
